@@ -1,0 +1,130 @@
+/* optimi_b200 — C ABI of the B200 (sm_100a) optimizer-step kernels.
+ *
+ * Each entry point replaces one of the reference's step back ends (the `_foreach_*`,
+ * `_single_param_*` and `_triton_*` functions its functional API dispatches to) for a whole list
+ * of tensors in one or a few kernel launches.  Conventions shared by every entry point:
+ *
+ *   - `n_tensors` tensors; `numels[i]` is the element count of tensor i (host array).
+ *   - Every `void* const* xs` is a HOST array of `n_tensors` DEVICE pointers.  All tensors of one
+ *     call live on the current device, are contiguous, and share one storage type `dtype`
+ *     (OPTIMI_F32 / OPTIMI_BF16 / OPTIMI_F16).  Parameters, gradients and states of a tensor
+ *     have the same element count.
+ *   - Everything is updated in place.  Gradients are only read (the reference's foreach path
+ *     leaves them clobbered; callers of either must not reuse them after the step).
+ *   - Scalars arrive as the doubles the reference's functional layer computes on the host
+ *     (debiased betas, folded weight-decay factor, ...) and are narrowed to fp32 inside, exactly
+ *     where the reference's ATen ops narrow them.
+ *   - Arithmetic replays the reference's op sequence in registers: one fp32 computation and one
+ *     rounding to the storage type per ATen op, so low-precision results are bit-identical to
+ *     the reference's foreach path on the same device (StableAdamW up to the summation order of
+ *     its per-tensor mean).
+ *   - `kahan_comps == NULL` (or kahan_sum == 0) selects the plain update.
+ *   - `update_parameters == 0` is the optimizer-accumulation micro-step: state averages advance,
+ *     weight decay and the parameter update are skipped, parameters and Kahan buffers untouched.
+ *   - `stream` is a cudaStream_t (NULL = the legacy default stream).  Calls only enqueue work.
+ *   - Return value: OPTIMI_OK or a negative OPTIMI_ERR_*; optimi_b200_last_error() gives the text
+ *     of the calling thread's last failure.  Nothing aborts, nothing traps on the device.
+ *   - No entry point allocates or frees device memory.
+ */
+#ifndef OPTIMI_B200_H
+#define OPTIMI_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define OPTIMI_F32 0
+#define OPTIMI_BF16 1
+#define OPTIMI_F16 2
+
+#define OPTIMI_OK 0
+#define OPTIMI_ERR_INVALID_ARGUMENT (-1)
+#define OPTIMI_ERR_CUDA (-2)
+#define OPTIMI_ERR_WORKSPACE_TOO_SMALL (-3)
+
+const char* optimi_b200_last_error(void);
+
+/* Library version as major*10000 + minor*100 + patch. */
+int optimi_b200_version(void);
+
+/* Adam / AdamW.  Replaces _foreach_adam (optimi/adam.py:399-453), _single_param_adam
+ * (optimi/adam.py:354-396) and the Triton launchers (optimi/adam.py:533-630); called where
+ * adam() picks its back end (optimi/adam.py:278-309).  `weight_decay` is the factor adam()
+ * has already folded (1 - lr*wd or 1 - lr/max_lr*wd when decouple_wd != 0, the raw L2
+ * coefficient otherwise; optimi/adam.py:269-273). */
+int optimi_b200_adam(int n_tensors, void* const* params, void* const* grads, void* const* exp_avgs,
+                     void* const* exp_avg_sqs, void* const* kahan_comps, const int64_t* numels, int dtype,
+                     double lr, double beta1_comp, double beta2_hat, double beta2_comp, double weight_decay,
+                     double eps, int decouple_wd, int kahan_sum, int update_parameters, void* stream);
+
+/* Lion.  Replaces _foreach_lion (optimi/lion.py:341-380), _single_param_lion (optimi/lion.py:301-338)
+ * and the Triton launchers (optimi/lion.py:453-530).  `weight_decay` is the folded factor
+ * (optimi/lion.py:227-231), 0 for none. */
+int optimi_b200_lion(int n_tensors, void* const* params, void* const* grads, void* const* exp_avgs,
+                     void* const* kahan_comps, const int64_t* numels, int dtype, double lr, double beta1_comp,
+                     double beta2_comp, double weight_decay, int kahan_sum, int update_parameters, void* stream);
+
+/* SGD with optional momentum / dampening.  Replaces _foreach_sgd (optimi/sgd.py:375-421),
+ * _single_param_sgd (optimi/sgd.py:329-372) and the Triton launchers (optimi/sgd.py:501-584).
+ * `exp_avgs` may be NULL when momentum == 0. */
+int optimi_b200_sgd(int n_tensors, void* const* params, void* const* grads, void* const* exp_avgs,
+                    void* const* kahan_comps, const int64_t* numels, int dtype, double lr, double momentum,
+                    double weight_decay, int dampening, int decouple_wd, int kahan_sum, int update_parameters,
+                    void* stream);
+
+/* StableAdamW.  Replaces _foreach_stableadamw (optimi/stableadamw.py:475-544),
+ * _single_param_stableadamw (optimi/stableadamw.py:421-472) and the two Triton kernels with
+ * their launchers (optimi/stableadamw.py:551-791).  The per-tensor RMS never leaves the device:
+ * pass A advances the averages and writes one partial sum per chunk, a one-block-per-tensor
+ * pass folds them in a fixed order into the clipped learning rate and weight-decay factor, pass
+ * B applies the update.  `weight_decay` is the RAW coefficient and `max_lr` the scheduled
+ * maximum (used when decouple_lr != 0), because the factor depends on the clipped learning
+ * rate (optimi/stableadamw.py:512-524).  `workspace` is device scratch of at least
+ * optimi_b200_stableadamw_workspace_bytes(...) bytes, 16-byte aligned; its contents need not be
+ * initialised and are overwritten. */
+size_t optimi_b200_stableadamw_workspace_bytes(int n_tensors, const int64_t* numels);
+int optimi_b200_stableadamw(int n_tensors, void* const* params, void* const* grads, void* const* exp_avgs,
+                            void* const* exp_avg_sqs, void* const* kahan_comps, const int64_t* numels, int dtype,
+                            double lr, double beta1_comp, double beta2_hat, double beta2_comp, double weight_decay,
+                            double eps, int decouple_lr, double max_lr, int kahan_sum, int update_parameters,
+                            void* workspace, size_t workspace_bytes, void* stream);
+
+/* Adan.  Replaces _foreach_adan (optimi/adan.py:472-546), _single_param_adan (optimi/adan.py:405-469)
+ * and the Triton launchers (optimi/adan.py:652-770).  `prev_grads` holds the NEGATED previous
+ * gradient (optimi/adan.py:109).  `weight_decay` is the folded factor 1 + lr*wd (Adan style,
+ * applied by division) or 1 - lr*wd (adam_wd != 0, applied by multiplication), 0 for none
+ * (optimi/adan.py:300-309). */
+int optimi_b200_adan(int n_tensors, void* const* params, void* const* grads, void* const* exp_avgs,
+                     void* const* exp_avg_diffs, void* const* exp_avg_sqs, void* const* prev_grads,
+                     void* const* kahan_comps, const int64_t* numels, int dtype, double lr, double beta1_comp,
+                     double beta2, double beta2_comp, double beta3_hat, double beta3_comp, double eps,
+                     double weight_decay, int adam_wd, int kahan_sum, int update_parameters, void* stream);
+
+/* RAdam.  Replaces _foreach_radam (optimi/radam.py:420-479), _single_param_radam
+ * (optimi/radam.py:368-417) and the Triton launchers (optimi/radam.py:567-686).
+ * `use_rect == 0` is the reference's rect=None (rho <= 5): momentum-only step. */
+int optimi_b200_radam(int n_tensors, void* const* params, void* const* grads, void* const* exp_avgs,
+                      void* const* exp_avg_sqs, void* const* kahan_comps, const int64_t* numels, int dtype,
+                      double lr, double beta1_comp, double beta2_hat, double beta2_comp, double weight_decay,
+                      double eps, int use_rect, double rect, int decouple_wd, int kahan_sum, int update_parameters,
+                      void* stream);
+
+/* Ranger (RAdam + Lookahead).  Replaces _foreach_ranger (optimi/ranger.py:476-561),
+ * _single_param_ranger (optimi/ranger.py:402-473) and the Triton launchers
+ * (optimi/ranger.py:674-810).  `do_lookahead != 0` on every k-th step (step % k == 0,
+ * optimi/ranger.py:537); the Kahan lookahead follows the foreach and Triton variants, which do
+ * not scale the slow-weight error by alpha. */
+int optimi_b200_ranger(int n_tensors, void* const* params, void* const* grads, void* const* exp_avgs,
+                       void* const* exp_avg_sqs, void* const* la_params, void* const* kahan_comps,
+                       const int64_t* numels, int dtype, double lr, double beta1_comp, double beta2_hat,
+                       double beta2_comp, double weight_decay, double eps, int use_rect, double rect,
+                       int do_lookahead, double alpha, int decouple_wd, int kahan_sum, int update_parameters,
+                       void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* OPTIMI_B200_H */

@@ -1,0 +1,82 @@
+"""ctypes binding of liboptimi_b200.so (the C ABI declared in include/optimi_b200.h).
+
+There is no fallback: if the library cannot be loaded (and cannot be built because nvcc is absent)
+importing this module raises, and a failing entry point raises ``RuntimeError`` with the library's
+own message.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+from . import build as _build
+
+OPTIMI_F32, OPTIMI_BF16, OPTIMI_F16 = 0, 1, 2
+DTYPE_CODE = {torch.float32: OPTIMI_F32, torch.bfloat16: OPTIMI_BF16, torch.float16: OPTIMI_F16}
+
+_P = ctypes.c_void_p  # host array of device pointers, or NULL
+_D = ctypes.c_double
+_I = ctypes.c_int
+
+# name -> argument types after (n_tensors) and the pointer lists; mirrors include/optimi_b200.h
+SIGNATURES = {
+    "optimi_b200_adam": [_I] + [_P] * 5 + [_P, _I] + [_D] * 6 + [_I] * 3 + [_P],
+    "optimi_b200_lion": [_I] + [_P] * 4 + [_P, _I] + [_D] * 4 + [_I] * 2 + [_P],
+    "optimi_b200_sgd": [_I] + [_P] * 4 + [_P, _I] + [_D] * 3 + [_I] * 4 + [_P],
+    "optimi_b200_stableadamw": [_I] + [_P] * 5 + [_P, _I] + [_D] * 6 + [_I, _D, _I, _I, _P, ctypes.c_size_t, _P],
+    "optimi_b200_adan": [_I] + [_P] * 7 + [_P, _I] + [_D] * 8 + [_I] * 3 + [_P],
+    "optimi_b200_radam": [_I] + [_P] * 5 + [_P, _I] + [_D] * 6 + [_I, _D] + [_I] * 3 + [_P],
+    "optimi_b200_ranger": [_I] + [_P] * 6 + [_P, _I] + [_D] * 6 + [_I, _D, _I, _D] + [_I] * 3 + [_P],
+}
+EXPORTS = list(SIGNATURES) + ["optimi_b200_last_error", "optimi_b200_version", "optimi_b200_stableadamw_workspace_bytes"]
+
+
+def _load() -> ctypes.CDLL:
+    path = _build.LIB
+    if not os.path.exists(path):
+        # a source checkout that has not been built yet: build once (needs nvcc), else fail loudly
+        path = _build.build()
+    lib = ctypes.CDLL(path)
+    for name, argtypes in SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.argtypes = argtypes
+        fn.restype = _I
+    lib.optimi_b200_last_error.restype = ctypes.c_char_p
+    lib.optimi_b200_last_error.argtypes = []
+    lib.optimi_b200_version.restype = _I
+    lib.optimi_b200_stableadamw_workspace_bytes.restype = ctypes.c_size_t
+    lib.optimi_b200_stableadamw_workspace_bytes.argtypes = [_I, _P]
+    return lib
+
+
+LIB = _load()
+LIB_PATH = _build.LIB
+
+
+def check(rc: int) -> None:
+    if rc != 0:
+        raise RuntimeError(f"optimi_b200 (code {rc}): {LIB.optimi_b200_last_error().decode()}")
+
+
+class PointerArray:
+    """A host array of device pointers for one tensor list (kept alive for the duration of a call)."""
+
+    __slots__ = ("arr",)
+
+    def __init__(self, tensors):
+        self.arr = (ctypes.c_void_p * len(tensors))(*[t.data_ptr() for t in tensors])
+
+    @property
+    def ptr(self):
+        return ctypes.cast(self.arr, ctypes.c_void_p)
+
+
+def pointer_list(tensors) -> PointerArray | None:
+    return None if tensors is None else PointerArray(tensors)
+
+
+def numel_array(tensors):
+    return (ctypes.c_int64 * len(tensors))(*[t.numel() for t in tensors])

@@ -1,0 +1,61 @@
+"""Builds the sm_100a kernel library in-tree: optimi_b200/lib/liboptimi_b200.so.
+
+    python -m optimi_b200.build [--force]
+
+nvcc cross-compiles without a GPU.  Flags that matter for parity: -fmad=false (the kernels fuse
+multiply-adds only where they say so with __fmaf_rn), default IEEE division and square root.
+"""
+
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+import sys
+
+PKG = os.path.dirname(os.path.abspath(__file__))
+SRC = os.path.join(PKG, "csrc", "optimi_b200.cu")
+DEPS = [SRC, os.path.join(PKG, "csrc", "mta_common.cuh"), os.path.join(PKG, "csrc", "optimizer_ops.cuh"),
+        os.path.join(os.path.dirname(PKG), "include", "optimi_b200.h")]  # fmt: skip
+LIB_DIR = os.path.join(PKG, "lib")
+LIB = os.path.join(LIB_DIR, "liboptimi_b200.so")
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-fmad=false", "-prec-div=true",
+    "-prec-sqrt=true", "-ftz=false", "-shared", "-Xcompiler", "-fPIC", "-Xcompiler", "-O2", "--use-local-env",
+]  # fmt: skip
+
+
+def find_nvcc() -> str:
+    for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and os.path.exists(cand):
+            return cand
+    raise RuntimeError("nvcc not found (set NVCC or add it to PATH)")
+
+
+def up_to_date() -> bool:
+    return os.path.exists(LIB) and all(os.path.getmtime(d) <= os.path.getmtime(LIB) for d in DEPS)
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    if not force and up_to_date():
+        return LIB
+    os.makedirs(LIB_DIR, exist_ok=True)
+    cmd = [find_nvcc(), *[f for f in NVCC_FLAGS if f != "--use-local-env"], "-o", LIB, SRC]
+    if verbose:
+        cmd.insert(1, "-Xptxas")
+        cmd.insert(2, "-v")
+    env = dict(os.environ)
+    # the image exports CC/CXX pointing at a wrapper; let nvcc use the system host compiler
+    if os.path.exists("/usr/bin/g++"):
+        cmd[1:1] = ["-ccbin", "/usr/bin/g++"]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError("nvcc failed:\n" + " ".join(cmd) + "\n" + res.stdout + res.stderr)
+    if verbose:
+        print(res.stderr)
+    return LIB
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

@@ -1,0 +1,535 @@
+// C ABI of the sm_100a optimizer-step kernels: argument checking, by-value table building,
+// kernel launches.  See include/optimi_b200.h for the contract of every entry point.
+#include "../../include/optimi_b200.h"
+
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <type_traits>
+
+#include "optimizer_ops.cuh"
+
+namespace optimi {
+
+// ---------------------------------------------------------------------------------------------
+// errors
+// ---------------------------------------------------------------------------------------------
+static thread_local char g_error[512] = "";
+
+static int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+static int check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(OPTIMI_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+  return OPTIMI_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// chunking
+// ---------------------------------------------------------------------------------------------
+// Elements per chunk for a list with `total` elements: large enough to amortise the block's set-up,
+// small enough that even one mid-sized tensor (a gradient-release launch) spreads over every SM.
+// OPTIMI_B200_CHUNK (a power of two between 4096 and 65536) overrides the choice, for tuning runs.
+static int pick_chunk(long long total) {
+  static const int forced = [] {
+    const char* s = getenv("OPTIMI_B200_CHUNK");
+    int v = s ? atoi(s) : 0;
+    return (v >= kMinChunk && v <= kMaxChunk && (v & (v - 1)) == 0) ? v : 0;
+  }();
+  if (forced) return forced;
+  int chunk = kMinChunk;
+  const long long want_blocks = 148LL * 16;
+  while (chunk < 16384 && total / (2LL * chunk) >= want_blocks) chunk *= 2;
+  return chunk;
+}
+
+static long long total_elements(int n, const int64_t* numels) {
+  long long t = 0;
+  for (int i = 0; i < n; i++) t += numels[i];
+  return t;
+}
+
+static Lerp make_lerp(double weight) {
+  Lerp l;
+  l.w = (float)weight;
+  l.omw = 1.0f - l.w;
+  l.low = fabsf(l.w) < 0.5f;
+  return l;
+}
+
+static int check_lists(const char* name, int n, const int64_t* numels, int dtype, int n_lists, void* const* const* lists,
+                       const bool* required, const char* const* list_names) {
+  if (n < 0) return fail(OPTIMI_ERR_INVALID_ARGUMENT, "%s: n_tensors=%d is negative", name, n);
+  if (dtype != OPTIMI_F32 && dtype != OPTIMI_BF16 && dtype != OPTIMI_F16)
+    return fail(OPTIMI_ERR_INVALID_ARGUMENT, "%s: unknown dtype code %d", name, dtype);
+  if (n == 0) return OPTIMI_OK;
+  if (!numels) return fail(OPTIMI_ERR_INVALID_ARGUMENT, "%s: numels is NULL", name);
+  for (int l = 0; l < n_lists; l++) {
+    if (required[l] && !lists[l]) return fail(OPTIMI_ERR_INVALID_ARGUMENT, "%s: list `%s` is NULL", name, list_names[l]);
+  }
+  for (int i = 0; i < n; i++) {
+    if (numels[i] < 0) return fail(OPTIMI_ERR_INVALID_ARGUMENT, "%s: numels[%d]=%lld is negative", name, i, (long long)numels[i]);
+    if (numels[i] == 0) continue;
+    for (int l = 0; l < n_lists; l++) {
+      if (required[l] && !lists[l][i])
+        return fail(OPTIMI_ERR_INVALID_ARGUMENT, "%s: `%s`[%d] is a NULL pointer for a tensor of %lld elements", name,
+                    list_names[l], i, (long long)numels[i]);
+    }
+  }
+  return OPTIMI_OK;
+}
+
+// Walks the tensor list, filling one by-value table after another and handing each to `launch`.
+template <int NL, class Launch>
+static int for_each_table(int n, const int64_t* numels, void* const* const (&lists)[NL], int chunk, Launch&& launch) {
+  using Table = MtaTable<NL>;
+  Table tab;  // ~30 KB on the host stack
+  int i = 0, chunk_base = 0;
+  while (i < n) {
+    int count = 0, chunks = 0;
+    tab.tensor_base = i;
+    tab.chunk_base = chunk_base;
+    tab.chunk_elems = chunk;
+    while (i < n && count < Table::CAP) {
+      const long long c = (numels[i] + chunk - 1) / chunk;
+      if ((long long)chunks + c > 0x7fffffffLL - 1) break;
+      for (int l = 0; l < NL; l++) tab.ptr[l][count] = lists[l] ? lists[l][i] : nullptr;
+      tab.numel[count] = numels[i];
+      tab.chunk_start[count] = chunks;
+      chunks += (int)c;
+      count++;
+      i++;
+    }
+    if (count == 0) return fail(OPTIMI_ERR_INVALID_ARGUMENT, "tensor %d has too many elements for one launch", i);
+    tab.chunk_start[count] = chunks;
+    tab.n_tensors = count;
+    if (chunks > 0) {
+      int rc = launch(tab, chunks);
+      if (rc != OPTIMI_OK) return rc;
+    }
+    chunk_base += chunks;
+  }
+  return OPTIMI_OK;
+}
+
+template <typename T, class Op>
+static int launch_op(const char* name, int n, const int64_t* numels, void* const* const (&lists)[Op::NL],
+                     const typename Op::Args& args, cudaStream_t stream) {
+  const int chunk = pick_chunk(total_elements(n, numels));
+  return for_each_table<Op::NL>(n, numels, lists, chunk, [&](const MtaTable<Op::NL>& tab, int chunks) {
+    mta_kernel<T, Op><<<chunks, kThreads, 0, stream>>>(tab, args);
+    return check_launch(name);
+  });
+}
+
+// Picks the instantiation for (dtype, kahan, update).  Kahan compensation exists only for the
+// 16-bit storage types, as in the reference (e.g. optimi/adam.py:421).
+template <template <bool, bool> class Op, class Lists, class Args>
+static int dispatch(const char* name, int dtype, bool kahan, bool update, int n, const int64_t* numels, const Lists& lists,
+                    const Args& args, cudaStream_t stream) {
+#define OPTIMI_GO(T)                                                                                   \
+  do {                                                                                                 \
+    if (!update) return launch_op<T, Op<false, false>>(name, n, numels, lists, args, stream);          \
+    if (kahan) return launch_op<T, Op<true, true>>(name, n, numels, lists, args, stream);              \
+    return launch_op<T, Op<false, true>>(name, n, numels, lists, args, stream);                        \
+  } while (0)
+  switch (dtype) {
+    case OPTIMI_F32:
+      if (!update) return launch_op<float, Op<false, false>>(name, n, numels, lists, args, stream);
+      return launch_op<float, Op<false, true>>(name, n, numels, lists, args, stream);
+    case OPTIMI_BF16: OPTIMI_GO(__nv_bfloat16);
+    case OPTIMI_F16: OPTIMI_GO(__half);
+  }
+#undef OPTIMI_GO
+  return fail(OPTIMI_ERR_INVALID_ARGUMENT, "%s: unknown dtype code %d", name, dtype);
+}
+
+// ---------------------------------------------------------------------------------------------
+// StableAdamW kernels
+// ---------------------------------------------------------------------------------------------
+struct StableMomentsArgs {
+  Lerp l1;
+  float beta2_hat, beta2_comp, eps_sq;  // eps_sq: eps^2 rounded to the storage type
+};
+
+// Pass A.  lists: 0 g, 1 m, 2 v.  Advances both averages (optimi/stableadamw.py:499-501) and, when
+// REDUCE, sums g^2 / max(v, eps^2) over the chunk (optimi/stableadamw.py:504-506) into
+// partial[chunk] — one double per chunk, written (not accumulated), so the scratch needs no
+// clearing and the result does not depend on block scheduling.
+template <typename T, bool REDUCE>
+__global__ void __launch_bounds__(kThreads) stable_moments_kernel(const __grid_constant__ MtaTable<3> tab,
+                                                                  const __grid_constant__ StableMomentsArgs a,
+                                                                  double* __restrict__ partial) {
+  constexpr int V = VecN<T>::N;
+  const Span s = locate(tab, blockIdx.x);
+  T* p[3];
+  const bool aligned = chunk_pointers<T, 3>(tab, s, p);
+  double acc = 0.0;
+
+  auto body = [&](auto width, int i) {
+    constexpr int N = decltype(width)::value;
+    float g[N], m[N], v[N];
+    Pack<T, N>::load(p[0] + i, g);
+    Pack<T, N>::load(p[1] + i, m);
+    Pack<T, N>::load(p[2] + i, v);
+    float part = 0.f;
+#pragma unroll
+    for (int j = 0; j < N; j++) {
+      adam_moments<T>(m[j], v[j], g[j], a.l1, a.beta2_hat, a.beta2_comp);
+      if (REDUCE) {
+        const float x = rnd<T>(fmaxf(v[j], a.eps_sq));
+        const float gg = rnd<T>(__fmul_rn(g[j], g[j]));
+        part += rnd<T>(__fdiv_rn(gg, x));
+      }
+    }
+    Pack<T, N>::store(p[1] + i, m);
+    Pack<T, N>::store(p[2] + i, v);
+    if (REDUCE) acc += (double)part;
+  };
+
+  if (aligned) {
+    const int nvec = s.len / V;
+#pragma unroll 2
+    for (int i = threadIdx.x; i < nvec; i += kThreads) body(std::integral_constant<int, V>{}, i * V);
+    for (int i = nvec * V + threadIdx.x; i < s.len; i += kThreads) body(std::integral_constant<int, 1>{}, i);
+  } else {
+    for (int i = threadIdx.x; i < s.len; i += kThreads) body(std::integral_constant<int, 1>{}, i);
+  }
+
+  if (REDUCE) {
+    __shared__ double warp_sum[kThreads / 32];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, o);
+    if ((threadIdx.x & 31) == 0) warp_sum[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      double t = 0.0;
+#pragma unroll
+      for (int w = 0; w < kThreads / 32; w++) t += warp_sum[w];
+      partial[tab.chunk_base + blockIdx.x] = t;
+    }
+  }
+}
+
+struct StableFinalizeArgs {
+  double lr, weight_decay, max_lr;
+  int decouple_lr;
+};
+
+// One block per tensor: folds the tensor's chunk partials in a fixed order, then does on the device
+// what the reference does on the host after `.item()` (optimi/stableadamw.py:512-524): mean and
+// square root rounded to the storage type, -lr / max(1, rms) and the weight-decay factor in double.
+template <typename T>
+__global__ void __launch_bounds__(256) stable_finalize_kernel(const __grid_constant__ MtaTable<3> tab,
+                                                              const __grid_constant__ StableFinalizeArgs a,
+                                                              const double* __restrict__ partial,
+                                                              float2* __restrict__ tensor_scalars) {
+  const int t = blockIdx.x;
+  const int c0 = tab.chunk_start[t], c1 = tab.chunk_start[t + 1];
+  double acc = 0.0;
+  for (int c = c0 + threadIdx.x; c < c1; c += 256) acc += partial[tab.chunk_base + c];
+  __shared__ double warp_sum[8];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, o);
+  if ((threadIdx.x & 31) == 0) warp_sum[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double sum = 0.0;
+    for (int w = 0; w < 8; w++) sum += warp_sum[w];
+    const long long n = tab.numel[t];
+    float2 out = make_float2((float)(-a.lr), 1.0f);
+    if (n > 0) {
+      const float mean = rnd<T>((float)(sum / (double)n));
+      const float rms = rnd<T>(__fsqrt_rn(mean));
+      const double neg_lr = -a.lr / fmax(1.0, (double)rms);
+      const double wd = a.decouple_lr ? 1.0 + (neg_lr / a.max_lr) * a.weight_decay : 1.0 + neg_lr * a.weight_decay;
+      out = make_float2((float)neg_lr, (float)wd);
+    }
+    tensor_scalars[tab.tensor_base + t] = out;
+  }
+}
+
+// Pass B.  lists: 0 p, 1 m, 2 v, 3 k.
+template <typename T, bool KAHAN>
+__global__ void __launch_bounds__(kThreads) stable_update_kernel(const __grid_constant__ MtaTable<4> tab,
+                                                                 const __grid_constant__ StableUpdateArgs a,
+                                                                 const float2* __restrict__ tensor_scalars) {
+  constexpr int V = VecN<T>::N;
+  const Span s = locate(tab, blockIdx.x);
+  T* p[4];
+  const bool aligned = chunk_pointers<T, 4>(tab, s, p);
+  const float2 sc = tensor_scalars[tab.tensor_base + s.tensor];
+  if (aligned) {
+    const int nvec = s.len / V;
+#pragma unroll 2
+    for (int i = threadIdx.x; i < nvec; i += kThreads) stable_update_run<T, KAHAN, V>(p, i * V, a, sc.x, sc.y);
+    for (int i = nvec * V + threadIdx.x; i < s.len; i += kThreads) stable_update_run<T, KAHAN, 1>(p, i, a, sc.x, sc.y);
+  } else {
+    for (int i = threadIdx.x; i < s.len; i += kThreads) stable_update_run<T, KAHAN, 1>(p, i, a, sc.x, sc.y);
+  }
+}
+
+static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+static long long count_chunks(int n, const int64_t* numels, int chunk) {
+  long long c = 0;
+  for (int i = 0; i < n; i++) c += (numels[i] + chunk - 1) / chunk;
+  return c;
+}
+
+template <typename T>
+static float round_to_storage(double x);
+template <> float round_to_storage<float>(double x) { return (float)x; }
+template <> float round_to_storage<__nv_bfloat16>(double x) { return __bfloat162float(__float2bfloat16_rn((float)x)); }
+template <> float round_to_storage<__half>(double x) { return __half2float(__float2half_rn((float)x)); }
+
+template <typename T>
+static int stableadamw_typed(int n, void* const* params, void* const* grads, void* const* exp_avgs, void* const* exp_avg_sqs,
+                             void* const* kahan_comps, const int64_t* numels, double lr, double beta1_comp, double beta2_hat,
+                             double beta2_comp, double weight_decay, double eps, int decouple_lr, double max_lr, bool kahan,
+                             bool update, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+  const int chunk = pick_chunk(total_elements(n, numels));
+  StableMomentsArgs ma;
+  ma.l1 = make_lerp(beta1_comp);
+  ma.beta2_hat = (float)beta2_hat;
+  ma.beta2_comp = (float)beta2_comp;
+  // the reference keeps eps^2 as a 0-dim tensor of the storage type (optimi/stableadamw.py:119)
+  ma.eps_sq = round_to_storage<T>(eps * eps);
+
+  void* const* const lists_a[3] = {grads, exp_avgs, exp_avg_sqs};
+  if (!update) {
+    return for_each_table<3>(n, numels, lists_a, chunk, [&](const MtaTable<3>& tab, int chunks) {
+      stable_moments_kernel<T, false><<<chunks, kThreads, 0, stream>>>(tab, ma, nullptr);
+      return check_launch("optimi_b200_stableadamw (moments)");
+    });
+  }
+
+  const size_t scal_bytes = align_up((size_t)n * sizeof(float2), 16);
+  const size_t need = scal_bytes + (size_t)count_chunks(n, numels, chunk) * sizeof(double);
+  if (!workspace || workspace_bytes < need)
+    return fail(OPTIMI_ERR_WORKSPACE_TOO_SMALL, "optimi_b200_stableadamw: workspace of %zu bytes given, %zu needed",
+                workspace ? workspace_bytes : (size_t)0, need);
+  if (reinterpret_cast<uintptr_t>(workspace) & 15)
+    return fail(OPTIMI_ERR_INVALID_ARGUMENT, "optimi_b200_stableadamw: workspace is not 16-byte aligned");
+  float2* tensor_scalars = reinterpret_cast<float2*>(workspace);
+  double* partial = reinterpret_cast<double*>(reinterpret_cast<char*>(workspace) + scal_bytes);
+
+  StableFinalizeArgs fa;
+  fa.lr = lr;
+  fa.weight_decay = weight_decay;
+  fa.max_lr = max_lr;
+  fa.decouple_lr = decouple_lr;
+
+  int rc = for_each_table<3>(n, numels, lists_a, chunk, [&](const MtaTable<3>& tab, int chunks) {
+    stable_moments_kernel<T, true><<<chunks, kThreads, 0, stream>>>(tab, ma, partial);
+    int r = check_launch("optimi_b200_stableadamw (moments)");
+    if (r != OPTIMI_OK) return r;
+    stable_finalize_kernel<T><<<tab.n_tensors, 256, 0, stream>>>(tab, fa, partial, tensor_scalars);
+    return check_launch("optimi_b200_stableadamw (finalize)");
+  });
+  if (rc != OPTIMI_OK) return rc;
+
+  StableUpdateArgs ua;
+  ua.eps = (float)eps;
+  ua.has_wd = weight_decay != 0;
+  void* const* const lists_b[4] = {params, exp_avgs, exp_avg_sqs, kahan ? kahan_comps : nullptr};
+  return for_each_table<4>(n, numels, lists_b, chunk, [&](const MtaTable<4>& tab, int chunks) {
+    if (kahan) stable_update_kernel<T, true><<<chunks, kThreads, 0, stream>>>(tab, ua, tensor_scalars);
+    else stable_update_kernel<T, false><<<chunks, kThreads, 0, stream>>>(tab, ua, tensor_scalars);
+    return check_launch("optimi_b200_stableadamw (update)");
+  });
+}
+
+static int wd_mode_of(double weight_decay, int decouple_wd) {
+  if (weight_decay == 0) return kWdNone;
+  return decouple_wd ? kWdDecoupled : kWdL2;
+}
+
+static bool low_precision(int dtype) { return dtype == OPTIMI_BF16 || dtype == OPTIMI_F16; }
+
+}  // namespace optimi
+
+using namespace optimi;
+
+extern "C" {
+
+const char* optimi_b200_last_error(void) { return g_error; }
+
+int optimi_b200_version(void) { return 100; }
+
+int optimi_b200_adam(int n, void* const* params, void* const* grads, void* const* exp_avgs, void* const* exp_avg_sqs,
+                     void* const* kahan_comps, const int64_t* numels, int dtype, double lr, double beta1_comp,
+                     double beta2_hat, double beta2_comp, double weight_decay, double eps, int decouple_wd, int kahan_sum,
+                     int update_parameters, void* stream) {
+  const bool update = update_parameters != 0;
+  const bool kahan = update && kahan_sum && kahan_comps && low_precision(dtype);
+  void* const* const lists[5] = {params, grads, exp_avgs, exp_avg_sqs, kahan ? kahan_comps : nullptr};
+  const bool req[5] = {update, true, true, true, kahan};
+  static const char* const names[5] = {"params", "grads", "exp_avgs", "exp_avg_sqs", "kahan_comps"};
+  int rc = check_lists("optimi_b200_adam", n, numels, dtype, 5, lists, req, names);
+  if (rc != OPTIMI_OK || n == 0) return rc;
+  AdamArgs a;
+  a.l1 = make_lerp(beta1_comp);
+  a.beta2_hat = (float)beta2_hat;
+  a.beta2_comp = (float)beta2_comp;
+  a.wd = (float)weight_decay;
+  a.eps = (float)eps;
+  a.neg_lr = (float)(-lr);
+  a.wd_mode = wd_mode_of(weight_decay, decouple_wd);
+  return dispatch<AdamOp>("optimi_b200_adam", dtype, kahan, update, n, numels, lists, a, (cudaStream_t)stream);
+}
+
+int optimi_b200_radam(int n, void* const* params, void* const* grads, void* const* exp_avgs, void* const* exp_avg_sqs,
+                      void* const* kahan_comps, const int64_t* numels, int dtype, double lr, double beta1_comp,
+                      double beta2_hat, double beta2_comp, double weight_decay, double eps, int use_rect, double rect,
+                      int decouple_wd, int kahan_sum, int update_parameters, void* stream) {
+  return optimi_b200_ranger(n, params, grads, exp_avgs, exp_avg_sqs, nullptr, kahan_comps, numels, dtype, lr, beta1_comp,
+                            beta2_hat, beta2_comp, weight_decay, eps, use_rect, rect, 0, 0.0, decouple_wd, kahan_sum,
+                            update_parameters, stream);
+}
+
+int optimi_b200_ranger(int n, void* const* params, void* const* grads, void* const* exp_avgs, void* const* exp_avg_sqs,
+                       void* const* la_params, void* const* kahan_comps, const int64_t* numels, int dtype, double lr,
+                       double beta1_comp, double beta2_hat, double beta2_comp, double weight_decay, double eps, int use_rect,
+                       double rect, int do_lookahead, double alpha, int decouple_wd, int kahan_sum, int update_parameters,
+                       void* stream) {
+  const bool update = update_parameters != 0;
+  const bool kahan = update && kahan_sum && kahan_comps && low_precision(dtype);
+  const bool look = update && do_lookahead;
+  void* const* const lists[6] = {params, grads, exp_avgs, exp_avg_sqs, kahan ? kahan_comps : nullptr,
+                                 look ? la_params : nullptr};
+  const bool req[6] = {update, true, true, true, kahan, look};
+  static const char* const names[6] = {"params", "grads", "exp_avgs", "exp_avg_sqs", "kahan_comps", "la_params"};
+  const char* fn = la_params ? "optimi_b200_ranger" : "optimi_b200_radam";
+  int rc = check_lists(fn, n, numels, dtype, 6, lists, req, names);
+  if (rc != OPTIMI_OK || n == 0) return rc;
+  RangerArgs a;
+  a.l1 = make_lerp(beta1_comp);
+  a.beta2_hat = (float)beta2_hat;
+  a.beta2_comp = (float)beta2_comp;
+  a.wd = (float)weight_decay;
+  a.eps = (float)eps;
+  a.neg_lr = use_rect ? (float)(-lr * rect) : (float)(-lr);
+  a.alpha = (float)alpha;
+  a.wd_mode = wd_mode_of(weight_decay, decouple_wd);
+  a.use_rect = use_rect != 0;
+  a.lookahead = look;
+  return dispatch<RangerOp>(fn, dtype, kahan, update, n, numels, lists, a, (cudaStream_t)stream);
+}
+
+int optimi_b200_lion(int n, void* const* params, void* const* grads, void* const* exp_avgs, void* const* kahan_comps,
+                     const int64_t* numels, int dtype, double lr, double beta1_comp, double beta2_comp, double weight_decay,
+                     int kahan_sum, int update_parameters, void* stream) {
+  const bool update = update_parameters != 0;
+  const bool kahan = update && kahan_sum && kahan_comps && low_precision(dtype);
+  void* const* const lists[4] = {params, grads, exp_avgs, kahan ? kahan_comps : nullptr};
+  const bool req[4] = {update, true, true, kahan};
+  static const char* const names[4] = {"params", "grads", "exp_avgs", "kahan_comps"};
+  int rc = check_lists("optimi_b200_lion", n, numels, dtype, 4, lists, req, names);
+  if (rc != OPTIMI_OK || n == 0) return rc;
+  LionArgs a;
+  a.l1 = make_lerp(beta1_comp);
+  a.l2 = make_lerp(beta2_comp);
+  a.wd = (float)weight_decay;
+  a.neg_lr = (float)(-lr);
+  a.wd_mode = weight_decay != 0 ? kWdDecoupled : kWdNone;
+  return dispatch<LionOp>("optimi_b200_lion", dtype, kahan, update, n, numels, lists, a, (cudaStream_t)stream);
+}
+
+int optimi_b200_sgd(int n, void* const* params, void* const* grads, void* const* exp_avgs, void* const* kahan_comps,
+                    const int64_t* numels, int dtype, double lr, double momentum, double weight_decay, int dampening,
+                    int decouple_wd, int kahan_sum, int update_parameters, void* stream) {
+  const bool update = update_parameters != 0;
+  const bool kahan = update && kahan_sum && kahan_comps && low_precision(dtype);
+  const bool has_m = momentum != 0;
+  if (!has_m && !update) return OPTIMI_OK;  // nothing to accumulate into (optimi/sgd.py:352-360)
+  void* const* const lists[4] = {params, grads, has_m ? exp_avgs : nullptr, kahan ? kahan_comps : nullptr};
+  const bool req[4] = {update, true, has_m, kahan};
+  static const char* const names[4] = {"params", "grads", "exp_avgs", "kahan_comps"};
+  int rc = check_lists("optimi_b200_sgd", n, numels, dtype, 4, lists, req, names);
+  if (rc != OPTIMI_OK || n == 0) return rc;
+  SgdArgs a;
+  a.damp = make_lerp(1 - momentum);
+  a.momentum = (float)momentum;
+  a.wd = (float)weight_decay;
+  a.neg_lr = (float)(-lr);
+  a.wd_mode = wd_mode_of(weight_decay, decouple_wd);
+  a.has_momentum = has_m;
+  a.dampening = dampening != 0;
+  return dispatch<SgdOp>("optimi_b200_sgd", dtype, kahan, update, n, numels, lists, a, (cudaStream_t)stream);
+}
+
+int optimi_b200_adan(int n, void* const* params, void* const* grads, void* const* exp_avgs, void* const* exp_avg_diffs,
+                     void* const* exp_avg_sqs, void* const* prev_grads, void* const* kahan_comps, const int64_t* numels,
+                     int dtype, double lr, double beta1_comp, double beta2, double beta2_comp, double beta3_hat,
+                     double beta3_comp, double eps, double weight_decay, int adam_wd, int kahan_sum, int update_parameters,
+                     void* stream) {
+  const bool update = update_parameters != 0;
+  const bool kahan = update && kahan_sum && kahan_comps && low_precision(dtype);
+  void* const* const lists[7] = {params, grads, exp_avgs, exp_avg_diffs, exp_avg_sqs, prev_grads, kahan ? kahan_comps : nullptr};
+  const bool req[7] = {update, true, true, true, true, true, kahan};
+  static const char* const names[7] = {"params", "grads", "exp_avgs", "exp_avg_diffs", "exp_avg_sqs", "prev_grads", "kahan_comps"};
+  int rc = check_lists("optimi_b200_adan", n, numels, dtype, 7, lists, req, names);
+  if (rc != OPTIMI_OK || n == 0) return rc;
+  AdanArgs a;
+  a.l1 = make_lerp(beta1_comp);
+  a.l2 = make_lerp(beta2_comp);
+  a.beta2 = (float)beta2;
+  a.beta3_hat = (float)beta3_hat;
+  a.beta3_comp = (float)beta3_comp;
+  a.eps = (float)eps;
+  a.neg_lr = (float)(-lr);
+  a.neg_lr_beta2 = (float)(-lr * beta2);
+  a.wd_mode = weight_decay == 0 ? 0 : (adam_wd ? 1 : 2);
+  // Adan-style decay divides by the factor; the reference's CUDA op multiplies by the reciprocal,
+  // taken in double precision and then narrowed to fp32
+  a.wd_mul = weight_decay == 0 ? 1.0f : (adam_wd ? (float)weight_decay : (float)(1.0 / weight_decay));
+  return dispatch<AdanOp>("optimi_b200_adan", dtype, kahan, update, n, numels, lists, a, (cudaStream_t)stream);
+}
+
+size_t optimi_b200_stableadamw_workspace_bytes(int n, const int64_t* numels) {
+  if (n <= 0 || !numels) return 16;
+  const int chunk = pick_chunk(total_elements(n, numels));
+  return align_up((size_t)n * sizeof(float2), 16) + (size_t)count_chunks(n, numels, chunk) * sizeof(double) + 16;
+}
+
+int optimi_b200_stableadamw(int n, void* const* params, void* const* grads, void* const* exp_avgs, void* const* exp_avg_sqs,
+                            void* const* kahan_comps, const int64_t* numels, int dtype, double lr, double beta1_comp,
+                            double beta2_hat, double beta2_comp, double weight_decay, double eps, int decouple_lr,
+                            double max_lr, int kahan_sum, int update_parameters, void* workspace, size_t workspace_bytes,
+                            void* stream) {
+  const bool update = update_parameters != 0;
+  const bool kahan = update && kahan_sum && kahan_comps && low_precision(dtype);
+  void* const* const lists[5] = {params, grads, exp_avgs, exp_avg_sqs, kahan ? kahan_comps : nullptr};
+  const bool req[5] = {update, true, true, true, kahan};
+  static const char* const names[5] = {"params", "grads", "exp_avgs", "exp_avg_sqs", "kahan_comps"};
+  int rc = check_lists("optimi_b200_stableadamw", n, numels, dtype, 5, lists, req, names);
+  if (rc != OPTIMI_OK || n == 0) return rc;
+  if (update && weight_decay != 0 && decouple_lr && !(max_lr > 0))
+    return fail(OPTIMI_ERR_INVALID_ARGUMENT, "optimi_b200_stableadamw: decouple_lr needs max_lr > 0");
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (dtype) {
+    case OPTIMI_F32:
+      return stableadamw_typed<float>(n, params, grads, exp_avgs, exp_avg_sqs, kahan_comps, numels, lr, beta1_comp, beta2_hat,
+                                      beta2_comp, weight_decay, eps, decouple_lr, max_lr, false, update, workspace,
+                                      workspace_bytes, s);
+    case OPTIMI_BF16:
+      return stableadamw_typed<__nv_bfloat16>(n, params, grads, exp_avgs, exp_avg_sqs, kahan_comps, numels, lr, beta1_comp,
+                                              beta2_hat, beta2_comp, weight_decay, eps, decouple_lr, max_lr, kahan, update,
+                                              workspace, workspace_bytes, s);
+    default:
+      return stableadamw_typed<__half>(n, params, grads, exp_avgs, exp_avg_sqs, kahan_comps, numels, lr, beta1_comp, beta2_hat,
+                                       beta2_comp, weight_decay, eps, decouple_lr, max_lr, kahan, update, workspace,
+                                       workspace_bytes, s);
+  }
+}
+
+}  // extern "C"

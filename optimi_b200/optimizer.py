@@ -1,0 +1,520 @@
+"""Optimizer classes with the reference's constructor, `step`, `zero_grad`, `state_dict` and
+gradient-release / optimizer-accumulation behaviour, stepping through the sm_100a kernels.
+
+One base class does all bookkeeping from a small per-optimizer description (which state tensors
+exist and how they start, which hyper-parameters go to the functional call); the reference spells
+the same logic out once per optimizer (optimi/optimizer.py:12-114 plus `_init_state`, `_init_group`
+and `step` of each optimi/<optimizer>.py).  What a checkpoint sees is unchanged: state keys, dtypes
+and shapes, `param_groups` entries including `setup` and the int32 CPU `step` tensor.
+"""
+
+from __future__ import annotations
+
+from collections.abc import Callable, Iterable
+from typing import Any
+from warnings import warn
+
+import torch
+from torch import Tensor
+from torch.optim.optimizer import Optimizer
+
+from . import functional as F
+
+LOW_PRECISION = (torch.float16, torch.bfloat16)
+
+
+def _check_range(name: str, value: float, shown: str | None = None):
+    if not 0.0 <= value < 1.0:
+        raise ValueError(f"Invalid {name} parameter: {shown or name}={value}")
+
+
+class OptimiOptimizer(Optimizer):
+    """Common behaviour of every optimi_b200 optimizer (mirror of optimi/optimizer.py:12-114)."""
+
+    # ---- per-optimizer description, overridden by subclasses ---------------------------------
+    _functional: Callable = None  # functional step
+    _list_args: tuple[str, ...] = ()  # functional list arguments after params, grads, in order; names of state keys
+    _state_arg_names: dict[str, str] = {}  # state key -> functional keyword
+    _counts_steps = True  # keeps a `step` counter (Lion and SGD do not)
+    _scalar_keys: tuple[str, ...] = ()  # param_group keys forwarded as keywords
+
+    def __init__(self, params: Iterable[Tensor] | Iterable[dict], defaults: dict[str, Any]):
+        if not 0.0 <= defaults["lr"]:
+            raise ValueError(f"Invalid learning rate: lr={defaults['lr']}")
+        if not 0.0 <= defaults["weight_decay"]:
+            raise ValueError(f"Invalid weight decay: weight_decay={defaults['weight_decay']}")
+        if defaults["decouple_lr"] and defaults["max_lr"] is None:
+            defaults["max_lr"] = defaults["lr"]
+        if defaults["max_lr"] is not None and not 0.0 <= defaults["max_lr"]:
+            raise ValueError(f"Invalid maximum learning rate: max_lr={defaults['max_lr']}")
+
+        if defaults["foreach"]:
+            warn(
+                "Parameter `foreach` is deprecated and has no effect: optimi_b200 always steps with its CUDA multi-tensor "
+                "kernels. Set `foreach=False` to silence this warning.",
+                category=DeprecationWarning,
+            )
+
+        super().__init__(params, defaults)
+
+        if self.defaults.get("decouple_lr", False):
+            high = [
+                g["weight_decay"]
+                for g in self.param_groups
+                if g.get("decouple_lr", self.defaults.get("decouple_lr", False)) and g.get("weight_decay", 0.0) >= 1e-3
+            ]
+            if high:
+                warn(
+                    f"You are using weight_decay up to {max(high)} which is potentially high for decouple_lr=True"
+                    f". Unlike decoupled weight decay, fully decoupled weight decay does not reduce weight decay by the learning rate.",
+                    category=UserWarning,
+                )
+
+        self._optimizer_accumulation = False
+        self._release_stream: torch.cuda.Stream | None = None
+        self._release_fence_queued = False
+
+        if self.defaults["gradient_release"]:
+            if self.defaults["foreach"]:
+                warn("Gradient release (gradient_release=True) and foreach (foreach=True) cannot be used together. Disabling foreach.", category=UserWarning)  # fmt: skip  # noqa: E501
+            self.defaults["foreach"] = False
+            for group in self.param_groups:
+                group["foreach"] = False
+                for p in group["params"]:
+                    self.state[p]["group"] = group
+
+    # ---- optimizer accumulation ---------------------------------------------------------------
+    @property
+    def optimizer_accumulation(self) -> bool:
+        "Accumulate gradients in optimizer states during gradient release instead of a full step."
+        return self._optimizer_accumulation
+
+    @optimizer_accumulation.setter
+    def optimizer_accumulation(self, optimizer_accumulation: bool):
+        self._optimizer_accumulation = optimizer_accumulation
+
+    # ---- state -------------------------------------------------------------------------------
+    def _new_state(self, group: dict[str, Any], state: dict[str, Any], param: Tensor) -> None:
+        """Creates the optimizer-specific state tensors of `param` (subclass hook)."""
+        raise NotImplementedError
+
+    def _kahan_state(self, group: dict[str, Any], param: Tensor) -> Tensor | None:
+        """Kahan compensation buffer: on by default for bf16/fp16 parameters (`kahan_sum=None`),
+        never for float32 (e.g. optimi/adam.py:100-106)."""
+        if (group["kahan_sum"] or group["kahan_sum"] is None) and param.dtype in LOW_PRECISION:
+            group["kahan_sum"] = True
+            return torch.zeros_like(param, memory_format=torch.preserve_format)
+        return None
+
+    def _init_state(self, group: dict[str, Any], state: dict[str, Any], param: Tensor) -> None:
+        if "kahan_comp" in state:
+            return
+        self._new_state(group, state, param)
+        state["kahan_comp"] = self._kahan_state(group, param)
+        if group["gradient_release"] and self._counts_steps:
+            state["step"] = torch.tensor(0, dtype=torch.int32)
+
+    def _setup_group(self, group: dict[str, Any]) -> None:
+        if not group["setup"]:
+            group["setup"] = True
+            if self._counts_steps:
+                group["step"] = torch.tensor(0, dtype=torch.int32)
+
+    def _keywords(self, group: dict[str, Any]) -> dict[str, Any]:
+        return {k: group[k] for k in self._scalar_keys}
+
+    # ---- step --------------------------------------------------------------------------------
+    @torch.no_grad()
+    def step(self, closure: Callable | None = None, param: Tensor | None = None):
+        """Performs a single optimization step on the whole model or on one parameter.
+
+        Args:
+            closure: A closure which reevaluates the model and returns the loss. Incompatible with
+                stepping a single `param`.
+            param: One parameter to step during the backward pass. Requires `gradient_release=True`
+                and hooks registered by `prepare_for_gradient_release`. Incompatible with `closure`.
+        """
+        loss = None
+        if closure is not None and param is None:
+            with torch.enable_grad():
+                loss = closure()
+
+        if param is None:
+            for group in self.param_groups:
+                lists: dict[str, list] = {k: [] for k in self._list_args}
+                params, grads = [], []
+                for p in group["params"]:
+                    if p.grad is None:
+                        continue
+                    state = self.state[p]
+                    self._init_state(group, state, p)
+                    params.append(p)
+                    grads.append(p.grad)
+                    for k in self._list_args:
+                        lists[k].append(state[k])
+                self._setup_group(group)
+                kw = self._keywords(group)
+                if self._counts_steps:
+                    kw["step"] = group["step"]
+                if not params:
+                    if self._counts_steps:
+                        group["step"].add_(1)  # the reference advances the counter before looking at the lists
+                    continue
+                type(self)._functional(
+                    params, grads, **{self._state_arg_names[k]: v for k, v in lists.items()}, **kw,
+                    kahan_sum=group["kahan_sum"], gradient_release=False, optimizer_accumulation=False,
+                )  # fmt: skip
+        else:
+            state = self.state[param]
+            group = state["group"]
+            self._init_state(group, state, param)
+            kw = self._keywords(group)
+            if self._counts_steps:
+                kw["step"] = state["step"]
+            stream = self._enter_release_stream(param)
+            type(self)._functional(
+                param, param.grad, **{self._state_arg_names[k]: state[k] for k in self._list_args}, **kw,
+                kahan_sum=group["kahan_sum"], gradient_release=True, optimizer_accumulation=self._optimizer_accumulation,
+                _stream=stream,
+            )  # fmt: skip
+            if stream is not None:
+                param.grad.record_stream(stream)
+        return loss
+
+    # ---- gradient release on a side stream ----------------------------------------------------
+    def use_release_stream(self, stream: torch.cuda.Stream | bool | None = True) -> None:
+        """Runs the per-parameter steps of gradient release on a side stream so that they overlap
+        with the rest of the backward pass.  `True` creates a stream, `None`/`False` goes back to
+        stepping on the stream the hook fires on (the reference's behaviour).
+
+        Ordering: each step waits for the gradient it consumes; the stream that runs the backward
+        pass waits for all side-stream steps when the backward pass ends, so code after
+        `loss.backward()` sees updated parameters without further synchronisation.
+        """
+        if stream is True:
+            stream = torch.cuda.Stream()
+        self._release_stream = stream or None
+
+    def _enter_release_stream(self, param: Tensor):
+        side = self._release_stream
+        if side is None:
+            return None
+        main = torch.cuda.current_stream(param.device)
+        side.wait_stream(main)
+        if not self._release_fence_queued:
+            self._release_fence_queued = True
+
+            def fence():
+                self._release_fence_queued = False
+                main.wait_stream(side)
+
+            try:
+                torch.autograd.Variable._execution_engine.queue_callback(fence)
+            except RuntimeError:
+                # not inside a backward pass (a manual step(param=...) call): fence right away
+                self._release_fence_queued = False
+                return None
+        return side
+
+    @torch._disable_dynamo
+    def zero_grad(self, set_to_none: bool = True, param: Tensor | None = None):
+        """Resets the gradients of all optimized parameters, or of `param` alone (gradient release)."""
+        if param is None:
+            super().zero_grad(set_to_none=set_to_none)
+        elif param.grad is not None:
+            if set_to_none:
+                param.grad = None
+            else:
+                if param.grad.grad_fn is not None:
+                    param.grad.detach_()
+                else:
+                    param.grad.requires_grad_(False)
+
+
+def _defaults(**kw) -> dict[str, Any]:
+    kw["setup"] = False
+    return kw
+
+
+class Adam(OptimiOptimizer):
+    """Adam optimizer, optionally with decoupled weight decay (AdamW).
+
+    Same arguments as the reference (optimi/adam.py:56-70): `params`, `lr`, `betas=(0.9, 0.99)`,
+    `weight_decay=0` (L2 unless `decouple_wd`/`decouple_lr`), `eps=1e-6`, `decouple_wd=False`,
+    `decouple_lr=False`, `max_lr=None`, `kahan_sum=None` (auto: on for bf16/fp16 parameters),
+    `foreach=None` and `triton=None` (accepted, ignored), `gradient_release=False`.
+    """
+
+    _functional = staticmethod(F.adam)
+    _list_args = ("exp_avg", "exp_avg_sq", "kahan_comp")
+    _state_arg_names = {"exp_avg": "exp_avgs", "exp_avg_sq": "exp_avg_sqs", "kahan_comp": "kahan_comps"}
+    _scalar_keys = ("lr", "beta1", "beta2", "weight_decay", "eps", "decouple_wd", "decouple_lr", "max_lr")
+
+    def __init__(
+        self,
+        params: Iterable[Tensor] | Iterable[dict],
+        lr: float,
+        betas: tuple[float, float] = (0.9, 0.99),
+        weight_decay: float = 0,
+        eps: float = 1e-6,
+        decouple_wd: bool = False,
+        decouple_lr: bool = False,
+        max_lr: float | None = None,
+        kahan_sum: bool | None = None,
+        foreach: bool | None = None,
+        triton: bool | None = None,
+        gradient_release: bool = False,
+    ):
+        _check_range("beta1", betas[0], "betas[0]")
+        _check_range("beta2", betas[1], "betas[1]")
+        if not 0.0 <= eps:
+            raise ValueError(f"Invalid epsilon: {eps=}")
+        super().__init__(params, _defaults(
+            lr=lr, beta1=betas[0], beta2=betas[1], eps=eps, weight_decay=weight_decay, decouple_wd=decouple_wd,
+            decouple_lr=decouple_lr, max_lr=max_lr, kahan_sum=kahan_sum, foreach=foreach, triton=triton,
+            gradient_release=gradient_release,
+        ))  # fmt: skip
+
+    def _new_state(self, group, state, param):
+        state["exp_avg"] = torch.zeros_like(param, memory_format=torch.preserve_format)
+        state["exp_avg_sq"] = torch.zeros_like(param, memory_format=torch.preserve_format)
+
+
+class AdamW(Adam):
+    """AdamW: Adam with decoupled weight decay, `weight_decay=1e-2` by default (optimi/adamw.py:48-75)."""
+
+    def __init__(
+        self,
+        params: Iterable[Tensor] | Iterable[dict],
+        lr: float,
+        betas: tuple[float, float] = (0.9, 0.99),
+        weight_decay: float = 1e-2,
+        eps: float = 1e-6,
+        decouple_lr: bool = False,
+        max_lr: float | None = None,
+        kahan_sum: bool | None = None,
+        foreach: bool | None = None,
+        triton: bool | None = None,
+        gradient_release: bool = False,
+    ):
+        super().__init__(
+            params=params, lr=lr, betas=betas, weight_decay=weight_decay, eps=eps, decouple_wd=True, decouple_lr=decouple_lr,
+            max_lr=max_lr, kahan_sum=kahan_sum, foreach=foreach, triton=triton, gradient_release=gradient_release,
+        )  # fmt: skip
+
+
+class RAdam(Adam):
+    """Rectified Adam (optimi/radam.py:57-71); same arguments as `Adam`."""
+
+    _functional = staticmethod(F.radam)
+
+
+class Ranger(OptimiOptimizer):
+    """Ranger: RAdam plus Lookahead every `k` steps with step size `alpha` (optimi/ranger.py:59-75).
+    Weight decay is decoupled by default."""
+
+    _functional = staticmethod(F.ranger)
+    _list_args = ("exp_avg", "exp_avg_sq", "la_param", "kahan_comp")
+    _state_arg_names = {"exp_avg": "exp_avgs", "exp_avg_sq": "exp_avg_sqs", "la_param": "la_params", "kahan_comp": "kahan_comps"}
+    _scalar_keys = ("lr", "beta1", "beta2", "weight_decay", "eps", "k", "alpha", "decouple_wd", "decouple_lr", "max_lr")
+
+    def __init__(
+        self,
+        params: Iterable[Tensor] | Iterable[dict],
+        lr: float,
+        betas: tuple[float, float] = (0.9, 0.99),
+        weight_decay: float = 0,
+        eps: float = 1e-6,
+        k: int = 6,
+        alpha: float = 0.5,
+        decouple_wd: bool = True,
+        decouple_lr: bool = False,
+        max_lr: float | None = None,
+        kahan_sum: bool | None = None,
+        foreach: bool | None = None,
+        triton: bool | None = None,
+        gradient_release: bool = False,
+    ):
+        _check_range("beta1", betas[0], "betas[0]")
+        _check_range("beta2", betas[1], "betas[1]")
+        if not 0.0 <= eps:
+            raise ValueError(f"Invalid epsilon: {eps=}")
+        super().__init__(params, _defaults(
+            lr=lr, beta1=betas[0], beta2=betas[1], eps=eps, weight_decay=weight_decay, k=k, alpha=alpha,
+            decouple_wd=decouple_wd, decouple_lr=decouple_lr, max_lr=max_lr, kahan_sum=kahan_sum, foreach=foreach,
+            triton=triton, gradient_release=gradient_release,
+        ))  # fmt: skip
+
+    def _new_state(self, group, state, param):
+        state["exp_avg"] = torch.zeros_like(param, memory_format=torch.preserve_format)
+        state["exp_avg_sq"] = torch.zeros_like(param, memory_format=torch.preserve_format)
+        state["la_param"] = param.data.clone()
+
+
+class Lion(OptimiOptimizer):
+    """Lion, evolved sign momentum (optimi/lion.py:56-68).  Weight decay is always decoupled."""
+
+    _functional = staticmethod(F.lion)
+    _list_args = ("exp_avg", "kahan_comp")
+    _state_arg_names = {"exp_avg": "exp_avgs", "kahan_comp": "kahan_comps"}
+    _counts_steps = False
+    _scalar_keys = ("lr", "beta1", "beta2", "weight_decay", "decouple_lr", "max_lr")
+
+    def __init__(
+        self,
+        params: Iterable[Tensor] | Iterable[dict],
+        lr: float,
+        betas: tuple[float, float] = (0.9, 0.99),
+        weight_decay: float = 0,
+        decouple_lr: bool = False,
+        max_lr: float | None = None,
+        kahan_sum: bool | None = None,
+        foreach: bool | None = None,
+        triton: bool | None = None,
+        gradient_release: bool = False,
+    ):
+        _check_range("beta1", betas[0], "betas[0]")
+        _check_range("beta2", betas[1], "betas[1]")
+        super().__init__(params, _defaults(
+            lr=lr, beta1=betas[0], beta2=betas[1], weight_decay=weight_decay, decouple_lr=decouple_lr, max_lr=max_lr,
+            kahan_sum=kahan_sum, foreach=foreach, triton=triton, gradient_release=gradient_release,
+        ))  # fmt: skip
+
+    def _new_state(self, group, state, param):
+        state["exp_avg"] = torch.zeros_like(param, memory_format=torch.preserve_format)
+
+
+class SGD(OptimiOptimizer):
+    """SGD with optional momentum, dampening and (decoupled) weight decay (optimi/sgd.py:63-78).
+    `torch_init=True` seeds the momentum buffer with the first gradient when dampening."""
+
+    _functional = staticmethod(F.sgd)
+    _list_args = ("exp_avg", "kahan_comp")
+    _state_arg_names = {"exp_avg": "exp_avgs", "kahan_comp": "kahan_comps"}
+    _counts_steps = False
+    _scalar_keys = ("lr", "momentum", "weight_decay", "dampening", "decouple_wd", "decouple_lr", "max_lr")
+
+    def __init__(
+        self,
+        params: Iterable[Tensor] | Iterable[dict],
+        lr: float,
+        momentum: float = 0,
+        weight_decay: float = 0,
+        dampening: bool = False,
+        decouple_wd: bool = False,
+        decouple_lr: bool = False,
+        max_lr: float | None = None,
+        torch_init: bool = False,
+        kahan_sum: bool | None = None,
+        foreach: bool | None = None,
+        triton: bool | None = None,
+        gradient_release: bool = False,
+    ):
+        if not 0.0 <= momentum < 1.0:
+            raise ValueError(f"Invalid momentum: {momentum=}")
+        super().__init__(params, _defaults(
+            lr=lr, momentum=momentum, weight_decay=weight_decay, dampening=dampening, decouple_wd=decouple_wd,
+            decouple_lr=decouple_lr, max_lr=max_lr, kahan_sum=kahan_sum, torch_init=torch_init, foreach=foreach,
+            triton=triton, gradient_release=gradient_release,
+        ))  # fmt: skip
+
+    def _new_state(self, group, state, param):
+        if group["dampening"] and group["torch_init"]:
+            # torch.optim.SGD seeds the buffer with the gradient after L2 decay (optimi/sgd.py:101-105)
+            state["exp_avg"] = param.grad.detach().clone()
+            if group["weight_decay"] != 0 and not group["decouple_lr"] and not group["decouple_wd"]:
+                state["exp_avg"].add_(param, alpha=group["weight_decay"])
+        elif group["momentum"] != 0:
+            state["exp_avg"] = torch.zeros_like(param, memory_format=torch.preserve_format)
+        else:
+            state["exp_avg"] = None
+
+
+class StableAdamW(OptimiOptimizer):
+    """StableAdamW: AdamW whose learning rate is clipped per tensor by the RMS of g^2/v
+    (optimi/stableadamw.py:76-89).  The RMS is reduced on the device; a step never synchronises."""
+
+    _functional = staticmethod(F.stableadamw)
+    _list_args = ("exp_avg", "exp_avg_sq", "eps_sq", "kahan_comp")
+    _state_arg_names = {"exp_avg": "exp_avgs", "exp_avg_sq": "exp_avg_sqs", "eps_sq": "eps_sqs", "kahan_comp": "kahan_comps"}
+    _scalar_keys = ("lr", "beta1", "beta2", "weight_decay", "eps", "decouple_lr", "max_lr")
+
+    def __init__(
+        self,
+        params: Iterable[Tensor] | Iterable[dict],
+        lr: float,
+        betas: tuple[float, float] = (0.9, 0.99),
+        weight_decay: float = 1e-2,
+        eps: float = 1e-6,
+        decouple_lr: bool = False,
+        max_lr: float | None = None,
+        kahan_sum: bool | None = None,
+        foreach: bool | None = None,
+        triton: bool | None = None,
+        gradient_release: bool = False,
+    ):
+        _check_range("beta1", betas[0], "betas[0]")
+        _check_range("beta2", betas[1], "betas[1]")
+        if not 0.0 <= eps:
+            raise ValueError(f"Invalid epsilon: {eps=}")
+        super().__init__(params, _defaults(
+            lr=lr, beta1=betas[0], beta2=betas[1], eps=eps, weight_decay=weight_decay, decouple_lr=decouple_lr,
+            max_lr=max_lr, kahan_sum=kahan_sum, foreach=foreach, triton=triton, gradient_release=gradient_release,
+        ))  # fmt: skip
+
+    def _new_state(self, group, state, param):
+        state["exp_avg"] = torch.zeros_like(param, memory_format=torch.preserve_format)
+        state["exp_avg_sq"] = torch.zeros_like(param, memory_format=torch.preserve_format)
+        # kept for checkpoint compatibility with the reference (optimi/stableadamw.py:119)
+        state["eps_sq"] = torch.tensor(group["eps"] ** 2, dtype=param.dtype, device=param.device)
+
+
+class Adan(OptimiOptimizer):
+    """Adan, adaptive Nesterov momentum (optimi/adan.py:62-76).  `kahan_sum` defaults to False here,
+    unlike the other optimizers, and the class always applies Adan-style weight decay: like the
+    reference it does not forward `adam_wd` to the functional step (optimi/adan.py:181-231)."""
+
+    _functional = staticmethod(F.adan)
+    _list_args = ("exp_avg", "exp_avg_diff", "exp_avg_sq", "prev_grad", "kahan_comp")
+    _state_arg_names = {"exp_avg": "exp_avgs", "exp_avg_diff": "exp_avg_diffs", "exp_avg_sq": "exp_avg_sqs",
+                        "prev_grad": "prev_grads", "kahan_comp": "kahan_comps"}  # fmt: skip
+    _scalar_keys = ("lr", "beta1", "beta2", "beta3", "weight_decay", "eps", "decouple_lr", "max_lr")
+
+    def __init__(
+        self,
+        params: Iterable[Tensor] | Iterable[dict],
+        lr: float,
+        betas: tuple[float, float, float] = (0.98, 0.92, 0.99),
+        weight_decay: float = 2e-2,
+        eps: float = 1e-6,
+        decouple_lr: bool = False,
+        max_lr: float | None = None,
+        adam_wd: bool = False,
+        kahan_sum: bool | None = False,
+        foreach: bool | None = None,
+        triton: bool | None = None,
+        gradient_release: bool = False,
+    ):
+        _check_range("beta1", betas[0], "betas[0]")
+        _check_range("beta2", betas[1], "betas[1]")
+        _check_range("beta3", betas[2], "betas[2]")
+        if not 0.0 <= eps:
+            raise ValueError(f"Invalid epsilon: {eps=}")
+        super().__init__(params, _defaults(
+            lr=lr, beta1=betas[0], beta2=betas[1], beta3=betas[2], eps=eps, weight_decay=weight_decay,
+            decouple_lr=decouple_lr, max_lr=max_lr, adam_wd=adam_wd, kahan_sum=kahan_sum, foreach=foreach, triton=triton,
+            gradient_release=gradient_release,
+        ))  # fmt: skip
+
+    def _new_state(self, group, state, param):
+        state["exp_avg"] = torch.zeros_like(param, memory_format=torch.preserve_format)
+        state["exp_avg_diff"] = torch.zeros_like(param, memory_format=torch.preserve_format)
+        state["exp_avg_sq"] = torch.zeros_like(param, memory_format=torch.preserve_format)
+        # negated first gradient, so the first gradient difference is zero (optimi/adan.py:109)
+        state["prev_grad"] = param.grad.clone().mul_(-1)
+
+    def _setup_group(self, group):
+        first = not group["setup"]
+        super()._setup_group(group)
+        if first and group["kahan_sum"]:
+            group["adam_wd"] = False  # optimi/adan.py:156-157

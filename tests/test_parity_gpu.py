@@ -1,0 +1,147 @@
+"""Parity of the CUDA kernels (through the classes and the C ABI) with the reference.
+
+1. Every golden case (reference run on a B200) replayed through optimi_b200: bit-exact for all
+   storage types, except
+     - StableAdamW: the per-tensor mean is summed in a different (fixed) order than the reference's
+       reduction, so float32 results agree to 1e-6 relative and 16-bit results to 1 ulp;
+     - the Ranger bf16 gradient-release golden, which follows `_single_param_ranger`'s variant of
+       the Kahan lookahead; the kernels follow the foreach/Triton variant and are checked
+       against the oracle instead.
+2. Larger seeded lists with ragged and misaligned tensors against the CPU oracle.
+"""
+
+import pytest
+import torch
+
+from cases import CASES, CASES_BY_NAME
+from helpers import (TORCH_DTYPE, compare_exact, golden_tensor, load_golden, run_b200_case, run_oracle_case, ulp_diff,
+                     within_ulps_of_scale)
+
+pytestmark = pytest.mark.gpu
+
+CUDA = load_golden("cuda")
+
+
+def _check_stable(case, got, want_of):
+    for key, t in got.items():
+        w = want_of(key)
+        t = t.detach().cpu().reshape(-1)
+        w = w.reshape(-1)
+        if case.dtype == "f32":
+            ok = (t.double() - w.double()).abs() <= 1e-9 + 1e-6 * w.double().abs()
+        else:
+            ok = within_ulps_of_scale(t, w, 1.0, 1e-3)
+        assert bool(ok.all()), f"{case.name} {key}: {int((~ok).sum())} elements off"
+
+
+@pytest.mark.parametrize("case", CASES, ids=lambda c: c.name)
+def test_kernels_match_reference_golden(case):
+    got = run_b200_case(case)
+    want_of = lambda k: golden_tensor(CUDA, case, k)  # noqa: E731
+    if case.opt == "stableadamw":
+        _check_stable(case, got, want_of)
+        return
+    if case.name == "gr_ranger_bf16k_dwd":
+        ref = run_oracle_case(case, single_param_lookahead=False)
+        bad = compare_exact(got, lambda k: ref.get(k), case.name)
+    else:
+        bad = compare_exact(got, want_of, case.name)
+    assert not bad, "\n".join(bad)
+
+
+@pytest.mark.parametrize("name", ["gr_adam_bf16k_dwd", "gr_adan_bf16k_wd", "gr_stableadamw_bf16k_dwd", "gr_lion_f32_dwd"])
+def test_release_stream_gives_same_result(name):
+    case = CASES_BY_NAME[name]
+    a = run_b200_case(case)
+    b = run_b200_case(case, release_stream=True)
+    for k in a:
+        assert torch.equal(a[k], b[k]), k
+
+
+# ----------------------------------------------------------------------------------------------
+# bigger, ragged, misaligned lists against the oracle
+# ----------------------------------------------------------------------------------------------
+BIG_SHAPES = [(1 << 20) + 3, 65536, 4096, 4097, 1, 100_003, (300, 257), 8, 0, 16384 * 3 + 5]
+
+
+def _big_inputs(dtype, seed, steps):
+    g = torch.Generator().manual_seed(seed)
+    params, grads = [], []
+    for shp in BIG_SHAPES:
+        shp = (shp,) if isinstance(shp, int) else shp
+        params.append((torch.randn(shp, generator=g) * 0.02).to(dtype))
+    scales = torch.exp(torch.randn(len(BIG_SHAPES), generator=g) + torch.log(torch.tensor(1e-3)))
+    for _ in range(steps):
+        grads.append([(torch.randn(p.shape, generator=g) * s).to(dtype) for p, s in zip(params, scales)])
+    return params, grads
+
+
+BIG = [
+    ("adam", dict(lr=3e-4, weight_decay=1e-5, decouple_lr=True), "bf16"),
+    ("adam", dict(lr=1e-3, weight_decay=1e-2), "f32"),
+    ("adamw", dict(lr=3e-4), "f16"),
+    ("lion", dict(lr=1e-4, weight_decay=0.1), "bf16"),
+    ("sgd", dict(lr=1e-2, momentum=0.9, weight_decay=1e-2), "bf16"),
+    ("sgd", dict(lr=1e-2, momentum=0.9, dampening=True, torch_init=True, weight_decay=1e-2), "f32"),
+    ("adan", dict(lr=3e-4, kahan_sum=True), "bf16"),
+    ("adan", dict(lr=3e-4), "f32"),
+    ("radam", dict(lr=3e-4, weight_decay=1e-2, decouple_wd=True), "bf16"),
+    ("ranger", dict(lr=3e-4, weight_decay=1e-2, k=3), "bf16"),
+    ("ranger", dict(lr=3e-4, k=3), "f32"),
+    ("stableadamw", dict(lr=3e-4), "bf16"),
+    ("stableadamw", dict(lr=3e-4), "f32"),
+]
+
+
+@pytest.mark.parametrize("opt,kw,dt", BIG, ids=[f"{o}-{d}-{i}" for i, (o, _, d) in enumerate(BIG)])
+@pytest.mark.parametrize("misalign", [False, True], ids=["aligned", "misaligned"])
+def test_kernels_match_oracle_on_ragged_lists(opt, kw, dt, misalign):
+    import warnings
+
+    import optimi_b200
+    from cases import CLASS_NAMES, STATE_NAMES
+    from oracle.port import OracleOptimizer
+
+    dtype = TORCH_DTYPE[dt]
+    steps = 7
+    params, grads = _big_inputs(dtype, 1234, steps)
+    oracle = OracleOptimizer(opt, [p.clone() for p in params], **kw)
+
+    def dev(t):
+        if not misalign:
+            return t.cuda()
+        # a view one element into a larger buffer: base address off the 16-byte grid
+        buf = torch.empty(t.numel() + 1, dtype=t.dtype, device="cuda")
+        v = buf[1:].view(t.shape)
+        v.copy_(t)
+        return v
+
+    dparams = [dev(p).requires_grad_(True) for p in params]
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        opt_gpu = getattr(optimi_b200, CLASS_NAMES[opt])(dparams, **kw)
+    for it in range(steps):
+        for p, g in zip(dparams, grads[it]):
+            p.grad = dev(g)
+        opt_gpu.step()
+        opt_gpu.zero_grad()
+        oracle.step([g.clone() for g in grads[it]])
+    torch.cuda.synchronize()
+    for i, p in enumerate(dparams):
+        pairs = [("param", p.detach().cpu(), oracle.params[i])]
+        for name in STATE_NAMES[opt]:
+            t = opt_gpu.state[p].get(name)
+            if t is not None and t.numel() == p.numel():
+                pairs.append((name, t.cpu(), oracle.state[i][name]))
+        for name, a, b in pairs:
+            if a.numel() == 0:
+                continue
+            if opt == "stableadamw":
+                if dt == "f32":
+                    ok = (a.double() - b.double()).abs() <= 1e-9 + 1e-6 * b.double().abs()
+                else:
+                    ok = within_ulps_of_scale(a, b, 1.0, 1e-3)
+                assert bool(ok.all()), f"tensor {i} {name}: {int((~ok).sum())} off"
+            else:
+                d = ulp_diff(a.reshape(-1), b.reshape(-1))
+                assert int(d.max()) == 0, f"tensor {i} {name}: {int((d > 0).sum())}/{d.numel()} differ, max {int(d.max())} ulp"
