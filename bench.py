@@ -1,0 +1,443 @@
+"""Benchmark of the optimizer-step hot path: AdamW bf16 + Kahan on Llama-3-8B parameter shapes.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl optimi_b200|reference] [--workload NAME]
+
+One "step" is one optimizer step over the whole parameter list (synthetic, seeded; no dataset).
+Prints ONE JSON line (rank 0).  For N > 1 launch under torchrun; the optimizer states are sharded
+ZeRO-1 style (optimi_b200.zero.ShardedOptimizer): each rank steps 1/N of the elements, then an NCCL
+all-gather distributes the updated bf16 parameters — total work is fixed, so scaling is "strong".
+
+Keys beyond the driver's contract:
+  roofline      dominant kernel against the HBM copy peak (MEASURED_PEAKS.json, else the fallback)
+  cpu_baseline  the reference's own foreach path on this host's cores (or the C oracle port when the
+                reference package is not present), on a bounded sample of the same workload
+  e2e           the same metric through the public API with gradients arriving from pinned host
+                memory every step and a small device-to-host read of the result
+  step_ms / gather_ms   device time of the local step and of the all-gather (N > 1)
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "AdamW bf16-Kahan step: Gparams/s & HBM GB/s vs 8 TB/s, 8B shapes, 1/2/4/8 GPU"
+UNIT = "Gparams/s"
+BYTES_PER_PARAM = 18  # read p,g,m,v,k (10 B) + write p,m,v,k (8 B), bf16 + Kahan
+FALLBACK_HBM_GBS = 6650.0
+
+HYPER = dict(lr=3e-4, betas=(0.9, 0.99), weight_decay=1e-5, eps=1e-6, decouple_lr=True)
+
+
+def llama_shapes(hidden, layers, ffn, q_heads, kv_heads, head_dim, vocab):
+    """Parameter shapes of a Llama-style decoder in Hugging Face order (untied output head)."""
+    shapes = [(vocab, hidden)]
+    for _ in range(layers):
+        shapes += [
+            (q_heads * head_dim, hidden), (kv_heads * head_dim, hidden), (kv_heads * head_dim, hidden),
+            (hidden, q_heads * head_dim), (ffn, hidden), (ffn, hidden), (hidden, ffn), (hidden,), (hidden,),
+        ]  # fmt: skip
+    shapes += [(hidden,), (vocab, hidden)]
+    return shapes
+
+
+WORKLOADS = {
+    "llama3-8b": lambda: llama_shapes(4096, 32, 14336, 32, 8, 128, 128256),
+    "llama-1.1b": lambda: llama_shapes(2048, 22, 5632, 32, 4, 64, 32000),
+    "llama-3b": lambda: llama_shapes(3072, 28, 8192, 24, 8, 128, 128256),
+    "llama-0.3b": lambda: llama_shapes(1024, 24, 2816, 16, 4, 64, 32000),  # small case for profiler captures
+    "tiny": lambda: llama_shapes(256, 2, 688, 4, 2, 64, 1024),
+}
+
+
+def numel(shape):
+    return math.prod(shape)
+
+
+def make_config(workload: str, n_gpus: int) -> dict:
+    """The `config` object of the JSON line; identical for both arms of one (workload, N)."""
+    shapes = WORKLOADS[workload]()
+    n_params = sum(numel(s) for s in shapes)
+    return {
+        "workload": f"AdamW bf16+Kahan, decouple_lr, {workload} parameter shapes ({n_params} params, {len(shapes)} tensors)",
+        "optimizer": "AdamW", "lr": HYPER["lr"], "weight_decay": HYPER["weight_decay"], "decouple_lr": True,
+        "sharding": "none" if n_gpus == 1 else f"ZeRO-1 over {n_gpus} ranks, NCCL all-gather of updated params",
+        "l2": "inputs larger than L2, no flush between steps: %.1f GB streamed per rank per step" % (BYTES_PER_PARAM * n_params / n_gpus / 1e9),
+    }  # fmt: skip
+
+
+def make_params(shapes, device, dtype, seed=0):
+    """2-D weights ~N(0, 0.02^2), 1-D (norm) weights = 1."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    out = []
+    for s in shapes:
+        if len(s) == 1:
+            out.append(torch.ones(s, device=device, dtype=dtype))
+        else:
+            out.append(torch.randn(s, device=device, dtype=torch.float32, generator=g).mul_(0.02).to(dtype))
+    return out
+
+
+def grad_scales(n, seed=0):
+    """Per-tensor gradient scale ~LogNormal(ln 1e-3, 1)."""
+    g = torch.Generator().manual_seed(seed)
+    return torch.exp(torch.randn(n, generator=g) + math.log(1e-3)).tolist()
+
+
+def fill_grad(t, scale, gen):
+    """N(0,1) * scale into `t`, chunked so the fp32 temporary stays small."""
+    flat = t.view(-1)
+    step = 1 << 26
+    for a in range(0, flat.numel(), step):
+        b = min(a + step, flat.numel())
+        flat[a:b] = torch.randn(b - a, device=t.device, dtype=torch.float32, generator=gen).mul_(scale).to(t.dtype)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")  # fmt: skip
+
+    def __init__(self, index: int):
+        self.index, self.proc = index, None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.index)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
+            )  # fmt: skip
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        self.result = None
+        if self.proc is None:
+            return
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if sm:
+            self.result = {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def dist_setup(n_gpus):
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    return world, rank, local
+
+
+def max_over_ranks(x: float, world: int, device) -> float:
+    if world == 1:
+        return x
+    import torch.distributed as dist
+
+    t = torch.tensor([x], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def barrier(world):
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU baseline: the reference's foreach path (or the oracle port) on the host cores
+# ------------------------------------------------------------------------------------------------
+def cpu_sample_shapes(workload):
+    """A bounded sample of the workload: the tensors of its first decoder layer."""
+    shapes = WORKLOADS[workload]()
+    return shapes[1:10]
+
+
+def time_cpu_reference(workload, steps, warmup, budget_s=25.0):
+    """Returns (Gparams/s, kind, cores, sample description).  One step = one optimizer step over the
+    sample, AdamW bf16 + Kahan with the benchmark's hyper-parameters, all host threads."""
+    shapes = cpu_sample_shapes(workload)
+    n = sum(numel(s) for s in shapes)
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    params = [p.requires_grad_(True) for p in make_params(shapes, "cpu", torch.bfloat16, seed=1)]
+    scales = grad_scales(len(shapes), seed=1)
+    gen = torch.Generator().manual_seed(1001)
+    grads = [torch.randn(s, generator=gen).mul_(sc).to(torch.bfloat16) for s, sc in zip(shapes, scales)]
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    kind = "port"
+    if os.path.isdir(os.path.join(ref_dir, "optimi")):
+        sys.path.insert(0, ref_dir)
+        try:
+            import warnings
+
+            import optimi  # the unmodified reference package
+
+            with warnings.catch_warnings():
+                warnings.simplefilter("ignore")
+                opt = optimi.AdamW(params, foreach=True, triton=False, **HYPER)
+            kind = "reference"
+
+            def one_step():
+                for p, g in zip(params, grads):
+                    p.grad = g.clone()  # the foreach path clobbers gradients
+                t0 = time.perf_counter()
+                opt.step()
+                return time.perf_counter() - t0
+        except Exception:
+            kind = "port"
+    if kind == "port":
+        from oracle.port import OracleOptimizer
+
+        opt = OracleOptimizer("adamw", [p.detach() for p in params], **HYPER)
+
+        def one_step():
+            gs = [g.clone() for g in grads]
+            t0 = time.perf_counter()
+            opt.step(gs)
+            return time.perf_counter() - t0
+
+    for _ in range(warmup):
+        one_step()
+    times, t_start = [], time.perf_counter()
+    for _ in range(steps):
+        times.append(one_step())
+        if time.perf_counter() - t_start > budget_s:
+            break
+    sec = statistics.median(times)
+    sample = f"first decoder layer of {workload}: {len(shapes)} tensors, {n} params, {len(times)} timed steps (median), grads re-cloned untimed"
+    return n / sec / 1e9, kind, cores, sample, sec * 1e3, len(times)
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    value, kind, cores, sample, ms, done = time_cpu_reference(args.workload, args.steps, args.warmup, budget_s=150.0)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": done,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": make_config(args.workload, args.gpus),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }  # fmt: skip
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------------------------------------
+# the optimi_b200 arm
+# ------------------------------------------------------------------------------------------------
+def run_b200_arm(args):
+    import optimi_b200
+    from optimi_b200 import _lib
+    from optimi_b200.zero import ShardedOptimizer
+
+    world, rank, local = dist_setup(args.gpus)
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node {args.gpus}")
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    dtype = torch.bfloat16
+    shapes = WORKLOADS[args.workload]()
+    n_params = sum(numel(s) for s in shapes)
+
+    params = [p.requires_grad_(True) for p in make_params(shapes, device, dtype, seed=0)]
+    if world == 1:
+        opt = optimi_b200.AdamW(params, **HYPER)
+        step_targets = params
+        sharded = None
+    else:
+        sharded = ShardedOptimizer(optimi_b200.AdamW, params, **HYPER)
+        opt = sharded
+        step_targets = sharded.shard_params
+    n_local = sum(t.numel() for t in step_targets)
+
+    # gradients resident in HBM for the `value` arm: one tensor per stepped tensor
+    scales = grad_scales(len(shapes), seed=0)
+    gen = torch.Generator(device=device).manual_seed(1000 + rank)
+    if sharded is None:
+        piece_scale = scales
+    else:
+        piece_scale = [scales[i] for b in sharded.buckets for (i, _, _) in b["pieces"]]
+    dev_grads = []
+    for t, sc in zip(step_targets, piece_scale):
+        g = torch.empty_like(t)
+        fill_grad(g, sc, gen)
+        dev_grads.append(g)
+
+    def step_resident():
+        if sharded is None:
+            opt.step()
+        else:
+            sharded.step(dev_grads)
+
+    for t, g in zip(step_targets, dev_grads):
+        t.grad = g
+
+    # ---- kernel-resident timing ---------------------------------------------------------------
+    for _ in range(max(args.warmup, 3)):
+        step_resident()
+    barrier(world)
+    stream = torch.cuda.current_stream(device)
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    launches0 = _lib.LIB.optimi_b200_launch_count()
+    with ClockSampler(local) as clocks:
+        barrier(world)
+        torch.cuda.profiler.start()  # lets a profiler started with --profile-from-start off see only the timed region
+        t_wall = time.perf_counter()
+        for k in range(args.steps):
+            ev[k][0].record(stream)
+            if sharded is None:
+                opt.step()
+                ev[k][1].record(stream)
+            else:
+                sharded.step_local(dev_grads)
+                ev[k][1].record(stream)
+                sharded.gather_params()
+            ev[k][2].record(stream)
+        barrier(world)
+        t_wall = time.perf_counter() - t_wall
+        torch.cuda.profiler.stop()
+    launches = _lib.LIB.optimi_b200_launch_count() - launches0
+    total_ms = ev[0][0].elapsed_time(ev[-1][2])
+    step_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / args.steps
+    gather_ms = sum(e[1].elapsed_time(e[2]) for e in ev) / args.steps
+    total_ms = max_over_ranks(total_ms, world, device)
+    step_ms_max = max_over_ranks(step_ms, world, device)
+    gather_ms_max = max_over_ranks(gather_ms, world, device)
+    ms_per_step = total_ms / args.steps
+    value = n_params / (ms_per_step * 1e-3) / 1e9
+
+    # ---- end to end: gradients from pinned host memory, result read back -----------------------
+    host_grads = [torch.empty(g.shape, dtype=g.dtype, pin_memory=True) for g in dev_grads]
+    for h, g in zip(host_grads, dev_grads):
+        h.copy_(g)
+    result_src = params[-2]  # the final norm weight: a small tensor every rank holds after the exchange
+    result_host = torch.empty(result_src.shape, dtype=result_src.dtype, pin_memory=True)
+    h2d_bytes = sum(h.numel() * h.element_size() for h in host_grads)
+    d2h_bytes = result_host.numel() * result_host.element_size()
+
+    def step_e2e():
+        for h, g in zip(host_grads, dev_grads):
+            g.copy_(h, non_blocking=True)
+        step_resident()
+        result_host.copy_(result_src.detach(), non_blocking=True)
+        torch.cuda.current_stream(device).synchronize()
+
+    e2e_steps = max(2, min(args.steps, 5))
+    step_e2e()
+    barrier(world)
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        step_e2e()
+    barrier(world)
+    e2e_s = max_over_ranks(time.perf_counter() - t0, world, device) / e2e_steps
+    e2e_value = n_params / e2e_s / 1e9
+
+    if rank != 0:
+        return
+
+    # ---- roofline of the dominant kernel (the step kernel) -------------------------------------
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_path):
+        with open(peaks_path) as fh:
+            peak, peak_kind = float(json.load(fh)["hbm_gbs"]), "measured"
+    else:
+        peak, peak_kind = FALLBACK_HBM_GBS, "fallback"
+    kernel_launches_per_step = max(1, launches // args.steps)
+    achieved = BYTES_PER_PARAM * n_local / (step_ms_max * 1e-3) / 1e9
+    traffic = None
+    traffic_path = os.path.join(ROOT, "profiles", "adamw_bf16_kahan_traffic.json")
+    if os.path.exists(traffic_path):
+        with open(traffic_path) as fh:
+            per_param = json.load(fh).get("dram_bytes_per_param")
+        if per_param:
+            traffic = per_param * n_local / kernel_launches_per_step
+    roofline = {
+        "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": traffic,
+        "peak_kind": f"of {peak_kind}", "frac_of_8TBs": achieved / 8000.0, "kernel": "mta_kernel<bf16, AdamOp<kahan,update>>",
+        "algorithmic_bytes_per_launch": BYTES_PER_PARAM * n_local / kernel_launches_per_step,
+        "launches_per_step": kernel_launches_per_step,
+    }  # fmt: skip
+
+    cpu = None
+    if world == 1 and not args.no_cpu_baseline:
+        v, kind, cores, sample, _, _ = time_cpu_reference(args.workload, 12, 2, budget_s=20.0)
+        cpu = {"value": v, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": make_config(args.workload, world),
+        "hbm_gbs": achieved, "step_ms": step_ms_max, "gather_ms": gather_ms_max, "wall_ms_per_step": t_wall * 1e3 / args.steps,
+        "roofline": roofline, "cpu_baseline": cpu,
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
+                "ms_per_step": e2e_s * 1e3, "steps": e2e_steps},
+        "gpu_launches": int(launches), "clocks": clocks.result, "library": os.path.relpath(_lib.LIB_PATH, ROOT),
+    }  # fmt: skip
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="optimi_b200", choices=["optimi_b200", "reference"])
+    ap.add_argument("--workload", default="llama3-8b", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_b200_arm(args)
+        if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+            import torch.distributed as dist
+
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

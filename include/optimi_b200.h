@@ -50,6 +50,9 @@ const char* optimi_b200_last_error(void);
 /* Library version as major*10000 + minor*100 + patch. */
 int optimi_b200_version(void);
 
+/* Number of CUDA kernels this library has launched in the calling process so far (all threads). */
+unsigned long long optimi_b200_launch_count(void);
+
 /* Adam / AdamW.  Replaces _foreach_adam (optimi/adam.py:399-453), _single_param_adam
  * (optimi/adam.py:354-396) and the Triton launchers (optimi/adam.py:533-630); called where
  * adam() picks its back end (optimi/adam.py:278-309).  `weight_decay` is the factor adam()
@@ -78,7 +81,7 @@ int optimi_b200_sgd(int n_tensors, void* const* params, void* const* grads, void
 /* StableAdamW.  Replaces _foreach_stableadamw (optimi/stableadamw.py:475-544),
  * _single_param_stableadamw (optimi/stableadamw.py:421-472) and the two Triton kernels with
  * their launchers (optimi/stableadamw.py:551-791).  The per-tensor RMS never leaves the device:
- * pass A advances the averages and writes one partial sum per chunk, a one-block-per-tensor
+ * pass A advances the averages and writes one partial sum per tile, a one-block-per-tensor
  * pass folds them in a fixed order into the clipped learning rate and weight-decay factor, pass
  * B applies the update.  `weight_decay` is the RAW coefficient and `max_lr` the scheduled
  * maximum (used when decouple_lr != 0), because the factor depends on the clipped learning

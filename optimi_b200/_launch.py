@@ -62,6 +62,9 @@ def group_by_device_and_dtype(lists: list[list[Tensor | None] | None]):
     keys: dict[tuple, list[int]] = {}
     for i, p in enumerate(params):
         keys.setdefault((p.device, p.dtype), []).append(i)
+    if len(keys) == 1:  # the usual case: one device, one dtype — no re-slicing
+        yield next(iter(keys)), [None if (lst is None or any(t is None for t in lst)) else lst for lst in lists]
+        return
     for key, idx in keys.items():
         sub = []
         for lst in lists:
@@ -73,17 +76,28 @@ def group_by_device_and_dtype(lists: list[list[Tensor | None] | None]):
         yield key, sub
 
 
+def _check_grads_only(name: str, params: list[Tensor], grads: list[Tensor]) -> None:
+    """The per-step check of a trusted call: gradients are the one list the optimizer did not create."""
+    for i, (p, g) in enumerate(zip(params, grads)):
+        if g.dtype != p.dtype or g.device != p.device or not _dense_like(g, p):
+            _check_group(name, [params, grads], ("params", "grads"))
+            raise RuntimeError(f"{name}: `grads`[{i}] does not match its parameter's dtype, device or layout")
+
+
 def launch(
     fn_name: str,
     lists: list[TensorList],
     list_names: Sequence[str],
     tail: Callable[[torch.device, torch.dtype, list[list[Tensor] | None]], tuple],
     stream: torch.cuda.Stream | None = None,
+    trusted: bool = False,
 ) -> None:
     """Calls entry point `fn_name` once per (device, dtype) group of `lists`.
 
     `tail(device, dtype, group_lists)` returns the arguments that follow `dtype` in the C
-    signature, without the trailing stream.
+    signature, without the trailing stream.  `trusted` (set by the optimizer classes, whose states
+    are created to match their parameters and whose parameters were checked when first seen) limits
+    the per-step checks to the gradients.
     """
     global launch_count
     lists = [as_list(x) for x in lists]
@@ -93,9 +107,14 @@ def launch(
         raise RuntimeError(f"{fn_name}: params must be tensors")
     fn = getattr(_lib.LIB, fn_name)
     for (device, dtype), sub in group_by_device_and_dtype(lists):
+        if device.type != "cuda":
+            raise RuntimeError(f"{fn_name}: parameters live on {device}; optimi_b200 steps CUDA tensors only (there is no CPU path)")
         if dtype not in _lib.DTYPE_CODE:
             raise RuntimeError(f"{fn_name}: unsupported parameter dtype {dtype} (float32, bfloat16 and float16 are)")
-        _check_group(fn_name, sub, list_names)
+        if trusted:
+            _check_grads_only(fn_name, sub[0], sub[1])
+        else:
+            _check_group(fn_name, sub, list_names)
         arrays = [_lib.pointer_list(x) for x in sub]
         numels = _lib.numel_array(sub[0])
         with torch.cuda.device(device):

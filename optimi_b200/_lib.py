@@ -14,6 +14,9 @@ import torch
 
 from . import build as _build
 
+# OPTIMI_B200_LIBRARY: load this prebuilt library instead of the in-tree one (kernel tuning runs)
+_OVERRIDE = os.environ.get("OPTIMI_B200_LIBRARY")
+
 OPTIMI_F32, OPTIMI_BF16, OPTIMI_F16 = 0, 1, 2
 DTYPE_CODE = {torch.float32: OPTIMI_F32, torch.bfloat16: OPTIMI_BF16, torch.float16: OPTIMI_F16}
 
@@ -31,14 +34,14 @@ SIGNATURES = {
     "optimi_b200_radam": [_I] + [_P] * 5 + [_P, _I] + [_D] * 6 + [_I, _D] + [_I] * 3 + [_P],
     "optimi_b200_ranger": [_I] + [_P] * 6 + [_P, _I] + [_D] * 6 + [_I, _D, _I, _D] + [_I] * 3 + [_P],
 }
-EXPORTS = list(SIGNATURES) + ["optimi_b200_last_error", "optimi_b200_version", "optimi_b200_stableadamw_workspace_bytes"]
+EXPORTS = list(SIGNATURES) + ["optimi_b200_last_error", "optimi_b200_version", "optimi_b200_launch_count", "optimi_b200_stableadamw_workspace_bytes"]
 
 
 def _load() -> ctypes.CDLL:
-    path = _build.LIB
-    if not os.path.exists(path):
-        # a source checkout that has not been built yet: build once (needs nvcc), else fail loudly
-        path = _build.build()
+    path = _OVERRIDE or _build.LIB
+    if not _OVERRIDE and not _build.up_to_date():
+        # not built yet, or built from other sources: build now (needs nvcc), else fail loudly
+        path = _build.build(force=True)
     lib = ctypes.CDLL(path)
     for name, argtypes in SIGNATURES.items():
         fn = getattr(lib, name)
@@ -47,13 +50,15 @@ def _load() -> ctypes.CDLL:
     lib.optimi_b200_last_error.restype = ctypes.c_char_p
     lib.optimi_b200_last_error.argtypes = []
     lib.optimi_b200_version.restype = _I
+    lib.optimi_b200_launch_count.restype = ctypes.c_ulonglong
+    lib.optimi_b200_launch_count.argtypes = []
     lib.optimi_b200_stableadamw_workspace_bytes.restype = ctypes.c_size_t
     lib.optimi_b200_stableadamw_workspace_bytes.argtypes = [_I, _P]
     return lib
 
 
 LIB = _load()
-LIB_PATH = _build.LIB
+LIB_PATH = _OVERRIDE or _build.LIB
 
 
 def check(rc: int) -> None:
@@ -67,7 +72,7 @@ class PointerArray:
     __slots__ = ("arr",)
 
     def __init__(self, tensors):
-        self.arr = (ctypes.c_void_p * len(tensors))(*[t.data_ptr() for t in tensors])
+        self.arr = (ctypes.c_void_p * len(tensors))(*map(torch.Tensor.data_ptr, tensors))
 
     @property
     def ptr(self):
@@ -79,4 +84,4 @@ def pointer_list(tensors) -> PointerArray | None:
 
 
 def numel_array(tensors):
-    return (ctypes.c_int64 * len(tensors))(*[t.numel() for t in tensors])
+    return (ctypes.c_int64 * len(tensors))(*map(torch.Tensor.numel, tensors))

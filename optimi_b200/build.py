@@ -8,6 +8,7 @@ multiply-adds only where they say so with __fmaf_rn), default IEEE division and 
 
 from __future__ import annotations
 
+import hashlib
 import os
 import shutil
 import subprocess
@@ -33,8 +34,23 @@ def find_nvcc() -> str:
     raise RuntimeError("nvcc not found (set NVCC or add it to PATH)")
 
 
+STAMP = LIB + ".srchash"
+
+
+def source_hash() -> str:
+    h = hashlib.sha256(" ".join(NVCC_FLAGS).encode())
+    for d in DEPS:
+        with open(d, "rb") as fh:
+            h.update(fh.read())
+    return h.hexdigest()
+
+
 def up_to_date() -> bool:
-    return os.path.exists(LIB) and all(os.path.getmtime(d) <= os.path.getmtime(LIB) for d in DEPS)
+    """True when the library was built from the sources as they are now (content hash, not mtime)."""
+    if not (os.path.exists(LIB) and os.path.exists(STAMP)):
+        return False
+    with open(STAMP) as fh:
+        return fh.read().strip() == source_hash()
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
@@ -54,6 +70,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
         raise RuntimeError("nvcc failed:\n" + " ".join(cmd) + "\n" + res.stdout + res.stderr)
     if verbose:
         print(res.stderr)
+    with open(STAMP, "w") as fh:
+        fh.write(source_hash())
     return LIB
 
 

@@ -2,11 +2,16 @@
 //
 // One launch covers a whole list of tensors.  The list is described by an MtaTable passed BY VALUE
 // in kernel parameter space (up to ~30 KB, which sm_70+ devices accept since CUDA 12.1), so a step
-// needs no device-side metadata buffer, no host-to-device copy and no allocation.  Tensors are cut
-// into fixed-size chunks; block b handles chunk b and finds its tensor with a binary search over
-// the prefix sum of chunk counts.  Within a chunk every thread moves 16 bytes per stream per
-// iteration (8 x bf16/fp16 or 4 x fp32), fully coalesced, with streaming cache hints since each
-// byte is touched once per step.
+// needs no device-side metadata buffer, no host-to-device copy and no allocation.
+//
+// Work decomposition, chosen by measurement on a B200: tensors are cut into small fixed tiles of
+// kThreads * U vectors (16 bytes each); one 256-thread block owns one tile, issues ALL of its loads
+// up front (U vectors per stream per thread), computes, stores and exits.  Millions of short-lived
+// blocks keep every SM's memory pipeline full without a persistent loop, and a register budget
+// around 50 leaves five blocks resident per SM.  Block b finds its tensor through a 256-entry
+// coarse index over the block range plus a short forward walk over the prefix sum of block counts
+// (a plain binary search over the table cost 10-20 % of the step: every probe is a dependent,
+// dynamically indexed read of kernel-parameter space).
 #pragma once
 
 #include <cuda_bf16.h>
@@ -16,59 +21,77 @@
 
 namespace optimi {
 
-constexpr int kThreads = 512;          // threads per block
-constexpr int kTableBytes = 30720;     // budget for one by-value table
-constexpr int kMinChunk = 4096;        // elements; multiple of kThreads * 8
-constexpr int kMaxChunk = 65536;
+#ifndef OPTIMI_THREADS
+#define OPTIMI_THREADS 256
+#endif
+constexpr int kThreads = OPTIMI_THREADS;  // threads per block
+constexpr int kTableBytes = 29440;  // budget for the per-tensor arrays of one by-value table
+constexpr int kBuckets = 256;       // coarse index over the tile range (see locate)
+#ifndef OPTIMI_TILES_PER_BLOCK
+#define OPTIMI_TILES_PER_BLOCK 1
+#endif
+constexpr int kTilesPerBlock = OPTIMI_TILES_PER_BLOCK;  // consecutive tiles one block walks through
 
 template <int NL>
 struct MtaTable {
   static constexpr int CAP = kTableBytes / (NL * 8 + 12);
-  void* ptr[NL][CAP];        // ptr[list][tensor]
+  void* ptr[NL][CAP];       // ptr[list][tensor]
   long long numel[CAP];
-  int chunk_start[CAP + 1];  // prefix sum of chunks per tensor; chunk_start[n_tensors] = grid size
+  int tile_start[CAP + 1];  // prefix sum of blocks per tensor; tile_start[n_tensors] = grid size
+  // bucket_tensor[b] = tensor that owns block (b << bucket_shift): a block starts its search there
+  // and walks forward, which for lists of large tensors is zero or one step
+  int bucket_tensor[kBuckets];
+  int bucket_shift;
   int n_tensors;
-  int chunk_elems;
-  int tensor_base;           // index of tensor 0 of this table within the caller's whole list
-  int chunk_base;            // index of chunk 0 of this table within the caller's whole list
+  int tensor_base;          // index of tensor 0 of this table within the caller's whole list
+  int tile_base;            // index of tile 0 of this table within the caller's whole list
 };
 
 // ---------------------------------------------------------------------------------------------
-// rounding to the storage type (round to nearest even), returned as float
-// ---------------------------------------------------------------------------------------------
-template <typename T> __device__ __forceinline__ float rnd(float x);
-template <> __device__ __forceinline__ float rnd<float>(float x) { return x; }
-template <> __device__ __forceinline__ float rnd<__nv_bfloat16>(float x) {
-  return __bfloat162float(__float2bfloat16_rn(x));
-}
-template <> __device__ __forceinline__ float rnd<__half>(float x) { return __half2float(__float2half_rn(x)); }
-
-// ---------------------------------------------------------------------------------------------
-// 16-byte vector access.  N = elements per vector.
+// storage types.  VecN<T>::N = elements per 16-byte vector.
 // ---------------------------------------------------------------------------------------------
 template <typename T> struct VecN;
 template <> struct VecN<float> { static constexpr int N = 4; };
 template <> struct VecN<__nv_bfloat16> { static constexpr int N = 8; };
 template <> struct VecN<__half> { static constexpr int N = 8; };
 
-__device__ __forceinline__ uint4 ld_stream(const void* p) { return __ldcs(reinterpret_cast<const uint4*>(p)); }
-__device__ __forceinline__ void st_stream(void* p, uint4 v) { __stcs(reinterpret_cast<uint4*>(p), v); }
+// Round an fp32 value to the storage type (nearest even) and return it as fp32.
+template <typename T> __device__ __forceinline__ float rnd(float x);
+template <> __device__ __forceinline__ float rnd<float>(float x) { return x; }
+template <> __device__ __forceinline__ float rnd<__nv_bfloat16>(float x) {
+  // one instruction: convert the pair {x, 0} to packed bf16x2; x lands in the upper half, which is
+  // exactly the fp32 bit pattern of the rounded value
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(x), "f"(0.0f));
+  return __uint_as_float(r);
+}
+template <> __device__ __forceinline__ float rnd<__half>(float x) { return __half2float(__float2half_rn(x)); }
 
-template <typename T, int N> struct Pack;
+// sqrt followed by rounding to the storage type.  For bf16 inputs the approximate square root
+// (relative error below 2^-22) rounds to the same bf16 value as the correctly rounded one: the
+// square root of a number with an 8-bit significand stays at least 2^-18 (relative) away from every
+// midpoint between two bf16 values.  fp16 and fp32 use the IEEE square root.
+template <typename T> __device__ __forceinline__ float sqrt_rnd(float x) { return rnd<T>(__fsqrt_rn(x)); }
+template <> __device__ __forceinline__ float sqrt_rnd<__nv_bfloat16>(float x) {
+  float r;
+  asm("sqrt.approx.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return rnd<__nv_bfloat16>(r);
+}
 
-// full vector
-template <> struct Pack<float, 4> {
-  static __device__ __forceinline__ void load(const float* p, float (&x)[4]) {
-    uint4 r = ld_stream(p);
+// Unpack a 16-byte vector into fp32 (exact) and pack fp32 values that are already representable in T.
+template <typename T> struct Pack;
+template <> struct Pack<float> {
+  static __device__ __forceinline__ void unpack(uint4 r, float (&x)[4]) {
     x[0] = __uint_as_float(r.x); x[1] = __uint_as_float(r.y); x[2] = __uint_as_float(r.z); x[3] = __uint_as_float(r.w);
   }
-  static __device__ __forceinline__ void store(float* p, const float (&x)[4]) {
-    st_stream(p, make_uint4(__float_as_uint(x[0]), __float_as_uint(x[1]), __float_as_uint(x[2]), __float_as_uint(x[3])));
+  static __device__ __forceinline__ uint4 pack(const float (&x)[4]) {
+    return make_uint4(__float_as_uint(x[0]), __float_as_uint(x[1]), __float_as_uint(x[2]), __float_as_uint(x[3]));
   }
+  static __device__ __forceinline__ float load1(const float* p) { return *p; }
+  static __device__ __forceinline__ void store1(float* p, float x) { *p = x; }
 };
-template <> struct Pack<__nv_bfloat16, 8> {
-  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&x)[8]) {
-    uint4 r = ld_stream(p);
+template <> struct Pack<__nv_bfloat16> {
+  static __device__ __forceinline__ void unpack(uint4 r, float (&x)[8]) {
     const uint32_t w[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
     for (int i = 0; i < 4; i++) {  // bf16 -> fp32 is a 16-bit shift
@@ -76,19 +99,20 @@ template <> struct Pack<__nv_bfloat16, 8> {
       x[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
     }
   }
-  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&x)[8]) {
+  static __device__ __forceinline__ uint4 pack(const float (&x)[8]) {
     uint32_t w[4];
 #pragma unroll
     for (int i = 0; i < 4; i++) {
       __nv_bfloat162 h = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
       w[i] = *reinterpret_cast<uint32_t*>(&h);
     }
-    st_stream(p, make_uint4(w[0], w[1], w[2], w[3]));
+    return make_uint4(w[0], w[1], w[2], w[3]);
   }
+  static __device__ __forceinline__ float load1(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+  static __device__ __forceinline__ void store1(__nv_bfloat16* p, float x) { *p = __float2bfloat16_rn(x); }
 };
-template <> struct Pack<__half, 8> {
-  static __device__ __forceinline__ void load(const __half* p, float (&x)[8]) {
-    uint4 r = ld_stream(p);
+template <> struct Pack<__half> {
+  static __device__ __forceinline__ void unpack(uint4 r, float (&x)[8]) {
     const uint32_t w[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
     for (int i = 0; i < 4; i++) {
@@ -96,69 +120,63 @@ template <> struct Pack<__half, 8> {
       x[2 * i] = f.x; x[2 * i + 1] = f.y;
     }
   }
-  static __device__ __forceinline__ void store(__half* p, const float (&x)[8]) {
+  static __device__ __forceinline__ uint4 pack(const float (&x)[8]) {
     uint32_t w[4];
 #pragma unroll
     for (int i = 0; i < 4; i++) {
       __half2 h = __floats2half2_rn(x[2 * i], x[2 * i + 1]);
       w[i] = *reinterpret_cast<uint32_t*>(&h);
     }
-    st_stream(p, make_uint4(w[0], w[1], w[2], w[3]));
+    return make_uint4(w[0], w[1], w[2], w[3]);
   }
-};
-// single element (ragged tails, tensors whose base address is not 16-byte aligned)
-template <> struct Pack<float, 1> {
-  static __device__ __forceinline__ void load(const float* p, float (&x)[1]) { x[0] = *p; }
-  static __device__ __forceinline__ void store(float* p, const float (&x)[1]) { *p = x[0]; }
-};
-template <> struct Pack<__nv_bfloat16, 1> {
-  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&x)[1]) { x[0] = __bfloat162float(*p); }
-  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&x)[1]) { *p = __float2bfloat16_rn(x[0]); }
-};
-template <> struct Pack<__half, 1> {
-  static __device__ __forceinline__ void load(const __half* p, float (&x)[1]) { x[0] = __half2float(*p); }
-  static __device__ __forceinline__ void store(__half* p, const float (&x)[1]) { *p = __float2half_rn(x[0]); }
+  static __device__ __forceinline__ float load1(const __half* p) { return __half2float(*p); }
+  static __device__ __forceinline__ void store1(__half* p, float x) { *p = __float2half_rn(x); }
 };
 
+// streaming 16-byte accesses: every byte is touched once per step
+template <typename T> __device__ __forceinline__ uint4 ldv(const T* p) { return __ldcs(reinterpret_cast<const uint4*>(p)); }
+template <typename T> __device__ __forceinline__ void stv(T* p, uint4 v) { __stcs(reinterpret_cast<uint4*>(p), v); }
+
 // ---------------------------------------------------------------------------------------------
-// fp32 building blocks with the exact formula of the ATen CUDA op they replay
+// scalar-weight lerp, at::native::lerp: |w| < 0.5 ? a + w*(b-a) : b - (b-a)*(1-w), multiply and add
+// fused.  Both branches are one fma of d = b-a: fma(d, w, a) or fma(d, -(1-w), b).
 // ---------------------------------------------------------------------------------------------
-// at::native::lerp with a scalar weight: |w| < 0.5 ? a + w*(b-a) : b - (b-a)*(1-w), multiply and
-// add fused.  `low` = (|w| < 0.5), `omw` = 1 - w, both uniform across the launch.
-__device__ __forceinline__ float lerp_op(float a, float b, float w, float omw, bool low) {
-  float d = __fsub_rn(b, a);
-  return low ? __fmaf_rn(w, d, a) : __fmaf_rn(-d, omw, b);
+struct Lerp {
+  float x;  // w when |w| < 0.5, else -(1-w)
+  int low;  // |w| < 0.5
+};
+__device__ __forceinline__ float lerp_op(float a, float b, const Lerp& l) {
+  return __fmaf_rn(__fsub_rn(b, a), l.x, l.low ? a : b);
 }
 
 // ---------------------------------------------------------------------------------------------
-// chunk location
+// tile location
 // ---------------------------------------------------------------------------------------------
 struct Span {
-  int tensor;         // index within the table
-  long long begin;    // first element of this block's chunk within the tensor
-  int len;            // elements in this chunk (<= chunk_elems)
+  int tensor;       // index within the table
+  long long begin;  // first element of this block's tile within the tensor
+  int len;          // elements in this tile (<= tile size)
 };
 
+// `block_elems` = elements one block covers (kTilesPerBlock tiles).  s.len is the number of elements
+// of the tensor left from s.begin, capped at block_elems.
 template <int NL>
-__device__ __forceinline__ Span locate(const MtaTable<NL>& tab, int chunk) {
-  int lo = 0, hi = tab.n_tensors;  // invariant: chunk_start[lo] <= chunk < chunk_start[hi]
-  while (hi - lo > 1) {
-    int mid = (lo + hi) >> 1;
-    if (tab.chunk_start[mid] <= chunk) lo = mid; else hi = mid;
-  }
+__device__ __forceinline__ Span locate(const MtaTable<NL>& tab, int block, int block_elems) {
+  int t = tab.bucket_tensor[block >> tab.bucket_shift];
+  while (tab.tile_start[t + 1] <= block) ++t;  // also skips empty tensors
   Span s;
-  s.tensor = lo;
-  s.begin = (long long)(chunk - tab.chunk_start[lo]) * tab.chunk_elems;
-  long long rem = tab.numel[lo] - s.begin;
-  s.len = rem < tab.chunk_elems ? (int)rem : tab.chunk_elems;
+  s.tensor = t;
+  s.begin = (long long)(block - tab.tile_start[t]) * block_elems;
+  const long long rem = tab.numel[t] - s.begin;
+  s.len = rem < block_elems ? (int)rem : block_elems;
   return s;
 }
 
-// Fetches the block's base pointers (advanced to the chunk) and reports whether every present
-// list is 16-byte aligned there; chunk offsets are multiples of 4096 elements, so only the
-// tensors' base addresses decide.
+// Fetches the block's base pointers (advanced to the tile) and reports whether every present list
+// is 16-byte aligned there; tile offsets are multiples of 16 bytes, so only the tensors' base
+// addresses decide.
 template <typename T, int NL>
-__device__ __forceinline__ bool chunk_pointers(const MtaTable<NL>& tab, const Span& s, T* (&p)[NL]) {
+__device__ __forceinline__ bool tile_pointers(const MtaTable<NL>& tab, const Span& s, T* (&p)[NL]) {
   uintptr_t bits = 0;
 #pragma unroll
   for (int l = 0; l < NL; l++) {
@@ -169,23 +187,122 @@ __device__ __forceinline__ bool chunk_pointers(const MtaTable<NL>& tab, const Sp
   return (bits & 15) == 0;
 }
 
-// Generic element-wise kernel: Op::run<T, N>(pointers, element offset, args) handles N consecutive
-// elements (N = vector width or 1).
+// ---------------------------------------------------------------------------------------------
+// Generic element-wise machinery.  An Op describes one optimizer variant:
+//   NL, U                     number of tensor lists, vectors per thread per list in a full tile
+//   Args                      uniform scalars of the launch
+//   Ctx / context(...)        per-tile values (per-tensor scalars for StableAdamW, empty otherwise)
+//   reads(l, args)            list l is loaded        (uniform across the launch)
+//   writes(l, args)           list l is stored back   (uniform across the launch)
+//   elem<T>(e, args, ctx)     the arithmetic for ONE element; e[l] is the element of list l as fp32
+//   kSumSlot                  index of an e[] slot whose values compute_vec sums up (-1: none)
+// ---------------------------------------------------------------------------------------------
+struct NoCtx {};
+
+template <int NL> struct Vecs { uint4 r[NL]; };
+
+template <typename T, class Op>
+__device__ __forceinline__ void load_vec(Vecs<Op::NL>& v, T* const (&p)[Op::NL], int i, const typename Op::Args& a) {
+#pragma unroll
+  for (int l = 0; l < Op::NL; l++)
+    if (Op::reads(l, a)) v.r[l] = ldv(p[l] + i);
+}
+
+template <typename T, class Op>
+__device__ __forceinline__ void store_vec(const Vecs<Op::NL>& v, T* const (&p)[Op::NL], int i, const typename Op::Args& a) {
+#pragma unroll
+  for (int l = 0; l < Op::NL; l++)
+    if (Op::writes(l, a)) stv(p[l] + i, v.r[l]);
+}
+
+template <typename T, class Op>
+__device__ __forceinline__ float compute_vec(Vecs<Op::NL>& v, const typename Op::Args& a, const typename Op::Ctx& ctx) {
+  constexpr int N = VecN<T>::N;
+  float x[Op::NL][N];
+#pragma unroll
+  for (int l = 0; l < Op::NL; l++) {
+    if (Op::reads(l, a)) {
+      Pack<T>::unpack(v.r[l], x[l]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < N; j++) x[l][j] = 0.f;
+    }
+  }
+  float sum = 0.f;
+#pragma unroll
+  for (int j = 0; j < N; j++) {
+    float e[Op::NL];
+#pragma unroll
+    for (int l = 0; l < Op::NL; l++) e[l] = x[l][j];
+    Op::template elem<T>(e, a, ctx);
+#pragma unroll
+    for (int l = 0; l < Op::NL; l++) x[l][j] = e[l];
+    if (Op::kSumSlot >= 0) sum += e[Op::kSumSlot < 0 ? 0 : Op::kSumSlot];
+  }
+#pragma unroll
+  for (int l = 0; l < Op::NL; l++)
+    if (Op::writes(l, a)) v.r[l] = Pack<T>::pack(x[l]);
+  return sum;
+}
+
+template <typename T, class Op>
+__device__ __forceinline__ float scalar_elem(T* const (&p)[Op::NL], int i, const typename Op::Args& a,
+                                             const typename Op::Ctx& ctx) {
+  float e[Op::NL];
+#pragma unroll
+  for (int l = 0; l < Op::NL; l++) e[l] = Op::reads(l, a) ? Pack<T>::load1(p[l] + i) : 0.f;
+  Op::template elem<T>(e, a, ctx);
+#pragma unroll
+  for (int l = 0; l < Op::NL; l++)
+    if (Op::writes(l, a)) Pack<T>::store1(p[l] + i, e[l]);
+  return Op::kSumSlot >= 0 ? e[Op::kSumSlot < 0 ? 0 : Op::kSumSlot] : 0.f;
+}
+
+// Processes the block's tile; returns this thread's share of the kSumSlot sum (0 without one).
+template <typename T, class Op>
+__device__ __forceinline__ double process_tile(const MtaTable<Op::NL>& tab, const typename Op::Args& args, Span& s) {
+  constexpr int V = VecN<T>::N;
+  constexpr int U = Op::U;
+  constexpr int TILE = kThreads * U * V;
+  s = locate(tab, blockIdx.x, TILE * kTilesPerBlock);
+  T* p[Op::NL];
+  const bool aligned = tile_pointers<T, Op::NL>(tab, s, p);
+  const typename Op::Ctx ctx = Op::context(tab, s, args);
+  double acc = 0.0;
+  int done = 0;
+  if (aligned) {
+    // full tiles: every load of the tile issued up front, then compute and store
+    for (; done + TILE <= s.len; done += TILE) {
+      Vecs<Op::NL> v[U];
+#pragma unroll
+      for (int u = 0; u < U; u++) load_vec<T, Op>(v[u], p, done + (u * kThreads + threadIdx.x) * V, args);
+#pragma unroll
+      for (int u = 0; u < U; u++) {
+        const float part = compute_vec<T, Op>(v[u], args, ctx);
+        store_vec<T, Op>(v[u], p, done + (u * kThreads + threadIdx.x) * V, args);
+        if (Op::kSumSlot >= 0) acc += (double)part;
+      }
+    }
+    // ragged end of the tensor: whole vectors, then single elements
+    const int nvec = (s.len - done) / V;
+    for (int i = threadIdx.x; i < nvec; i += kThreads) {
+      Vecs<Op::NL> v;
+      load_vec<T, Op>(v, p, done + i * V, args);
+      const float part = compute_vec<T, Op>(v, args, ctx);
+      store_vec<T, Op>(v, p, done + i * V, args);
+      if (Op::kSumSlot >= 0) acc += (double)part;
+    }
+    done += nvec * V;
+  }
+  for (int i = done + threadIdx.x; i < s.len; i += kThreads) acc += (double)scalar_elem<T, Op>(p, i, args, ctx);
+  return acc;
+}
+
 template <typename T, class Op>
 __global__ void __launch_bounds__(kThreads) mta_kernel(const __grid_constant__ MtaTable<Op::NL> tab,
                                                        const __grid_constant__ typename Op::Args args) {
-  constexpr int V = VecN<T>::N;
-  const Span s = locate(tab, blockIdx.x);
-  T* p[Op::NL];
-  const bool aligned = chunk_pointers<T, Op::NL>(tab, s, p);
-  if (aligned) {
-    const int nvec = s.len / V;
-#pragma unroll 2
-    for (int i = threadIdx.x; i < nvec; i += kThreads) Op::template run<T, V>(p, i * V, args);
-    for (int i = nvec * V + threadIdx.x; i < s.len; i += kThreads) Op::template run<T, 1>(p, i, args);
-  } else {
-    for (int i = threadIdx.x; i < s.len; i += kThreads) Op::template run<T, 1>(p, i, args);
-  }
+  Span s;
+  process_tile<T, Op>(tab, args, s);
 }
 
 }  // namespace optimi

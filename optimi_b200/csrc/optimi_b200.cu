@@ -2,6 +2,7 @@
 // kernel launches.  See include/optimi_b200.h for the contract of every entry point.
 #include "../../include/optimi_b200.h"
 
+#include <atomic>
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
@@ -26,42 +27,20 @@ static int fail(int code, const char* fmt, ...) {
   return code;
 }
 
+static std::atomic<unsigned long long> g_launches{0};
+
 static int check_launch(const char* what) {
+  g_launches.fetch_add(1, std::memory_order_relaxed);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(OPTIMI_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
   return OPTIMI_OK;
 }
 
-// ---------------------------------------------------------------------------------------------
-// chunking
-// ---------------------------------------------------------------------------------------------
-// Elements per chunk for a list with `total` elements: large enough to amortise the block's set-up,
-// small enough that even one mid-sized tensor (a gradient-release launch) spreads over every SM.
-// OPTIMI_B200_CHUNK (a power of two between 4096 and 65536) overrides the choice, for tuning runs.
-static int pick_chunk(long long total) {
-  static const int forced = [] {
-    const char* s = getenv("OPTIMI_B200_CHUNK");
-    int v = s ? atoi(s) : 0;
-    return (v >= kMinChunk && v <= kMaxChunk && (v & (v - 1)) == 0) ? v : 0;
-  }();
-  if (forced) return forced;
-  int chunk = kMinChunk;
-  const long long want_blocks = 148LL * 16;
-  while (chunk < 16384 && total / (2LL * chunk) >= want_blocks) chunk *= 2;
-  return chunk;
-}
-
-static long long total_elements(int n, const int64_t* numels) {
-  long long t = 0;
-  for (int i = 0; i < n; i++) t += numels[i];
-  return t;
-}
-
 static Lerp make_lerp(double weight) {
+  const float w = (float)weight;
   Lerp l;
-  l.w = (float)weight;
-  l.omw = 1.0f - l.w;
-  l.low = fabsf(l.w) < 0.5f;
+  l.low = fabsf(w) < 0.5f;
+  l.x = l.low ? w : -(1.0f - w);
   return l;
 }
 
@@ -88,44 +67,56 @@ static int check_lists(const char* name, int n, const int64_t* numels, int dtype
 }
 
 // Walks the tensor list, filling one by-value table after another and handing each to `launch`.
+// `tile` = elements per block.
 template <int NL, class Launch>
-static int for_each_table(int n, const int64_t* numels, void* const* const (&lists)[NL], int chunk, Launch&& launch) {
+static int for_each_table(int n, const int64_t* numels, void* const* const (&lists)[NL], int tile, Launch&& launch) {
   using Table = MtaTable<NL>;
   Table tab;  // ~30 KB on the host stack
-  int i = 0, chunk_base = 0;
+  int i = 0, tile_base = 0;
   while (i < n) {
-    int count = 0, chunks = 0;
+    int count = 0, tiles = 0;
     tab.tensor_base = i;
-    tab.chunk_base = chunk_base;
-    tab.chunk_elems = chunk;
+    tab.tile_base = tile_base;
     while (i < n && count < Table::CAP) {
-      const long long c = (numels[i] + chunk - 1) / chunk;
-      if ((long long)chunks + c > 0x7fffffffLL - 1) break;
+      const long long c = (numels[i] + tile - 1) / tile;
+      if ((long long)tiles + c > 0x7fffffffLL - 1) break;
       for (int l = 0; l < NL; l++) tab.ptr[l][count] = lists[l] ? lists[l][i] : nullptr;
       tab.numel[count] = numels[i];
-      tab.chunk_start[count] = chunks;
-      chunks += (int)c;
+      tab.tile_start[count] = tiles;
+      tiles += (int)c;
       count++;
       i++;
     }
     if (count == 0) return fail(OPTIMI_ERR_INVALID_ARGUMENT, "tensor %d has too many elements for one launch", i);
-    tab.chunk_start[count] = chunks;
+    tab.tile_start[count] = tiles;
     tab.n_tensors = count;
-    if (chunks > 0) {
-      int rc = launch(tab, chunks);
+    // coarse index: bucket b covers blocks [b << shift, (b+1) << shift)
+    int shift = 0;
+    while ((tiles >> shift) >= kBuckets) shift++;
+    tab.bucket_shift = shift;
+    for (int b = 0, t = 0; b < kBuckets; b++) {
+      const long long first = (long long)b << shift;
+      while (t + 1 < count && tab.tile_start[t + 1] <= first) t++;
+      tab.bucket_tensor[b] = t;
+    }
+    if (tiles > 0) {
+      int rc = launch(tab, tiles);
       if (rc != OPTIMI_OK) return rc;
     }
-    chunk_base += chunks;
+    tile_base += tiles;
   }
   return OPTIMI_OK;
 }
 
+// elements one block covers
+template <typename T, class Op>
+constexpr int tile_of() { return kThreads * Op::U * VecN<T>::N * kTilesPerBlock; }
+
 template <typename T, class Op>
 static int launch_op(const char* name, int n, const int64_t* numels, void* const* const (&lists)[Op::NL],
                      const typename Op::Args& args, cudaStream_t stream) {
-  const int chunk = pick_chunk(total_elements(n, numels));
-  return for_each_table<Op::NL>(n, numels, lists, chunk, [&](const MtaTable<Op::NL>& tab, int chunks) {
-    mta_kernel<T, Op><<<chunks, kThreads, 0, stream>>>(tab, args);
+  return for_each_table<Op::NL>(n, numels, lists, tile_of<T, Op>(), [&](const MtaTable<Op::NL>& tab, int tiles) {
+    mta_kernel<T, Op><<<tiles, kThreads, 0, stream>>>(tab, args);
     return check_launch(name);
   });
 }
@@ -155,67 +146,25 @@ static int dispatch(const char* name, int dtype, bool kahan, bool update, int n,
 // ---------------------------------------------------------------------------------------------
 // StableAdamW kernels
 // ---------------------------------------------------------------------------------------------
-struct StableMomentsArgs {
-  Lerp l1;
-  float beta2_hat, beta2_comp, eps_sq;  // eps_sq: eps^2 rounded to the storage type
-};
-
-// Pass A.  lists: 0 g, 1 m, 2 v.  Advances both averages (optimi/stableadamw.py:499-501) and, when
-// REDUCE, sums g^2 / max(v, eps^2) over the chunk (optimi/stableadamw.py:504-506) into
-// partial[chunk] — one double per chunk, written (not accumulated), so the scratch needs no
-// clearing and the result does not depend on block scheduling.
-template <typename T, bool REDUCE>
-__global__ void __launch_bounds__(kThreads) stable_moments_kernel(const __grid_constant__ MtaTable<3> tab,
-                                                                  const __grid_constant__ StableMomentsArgs a,
-                                                                  double* __restrict__ partial) {
-  constexpr int V = VecN<T>::N;
-  const Span s = locate(tab, blockIdx.x);
-  T* p[3];
-  const bool aligned = chunk_pointers<T, 3>(tab, s, p);
-  double acc = 0.0;
-
-  auto body = [&](auto width, int i) {
-    constexpr int N = decltype(width)::value;
-    float g[N], m[N], v[N];
-    Pack<T, N>::load(p[0] + i, g);
-    Pack<T, N>::load(p[1] + i, m);
-    Pack<T, N>::load(p[2] + i, v);
-    float part = 0.f;
+// Pass A with the per-tile sum: advances both averages and writes the tile's sum of
+// g^2 / max(v, eps^2) to partial[tile] — one double per tile, written (not accumulated), so the
+// scratch needs no clearing and the result does not depend on block scheduling.
+template <typename T>
+__global__ void __launch_bounds__(kThreads) stable_moments_sum_kernel(const __grid_constant__ MtaTable<4> tab,
+                                                                      const __grid_constant__ StableMomentsArgs a,
+                                                                      double* __restrict__ partial) {
+  Span s;
+  double acc = process_tile<T, StableMomentsOp<true>>(tab, a, s);
+  __shared__ double warp_sum[kThreads / 32];
 #pragma unroll
-    for (int j = 0; j < N; j++) {
-      adam_moments<T>(m[j], v[j], g[j], a.l1, a.beta2_hat, a.beta2_comp);
-      if (REDUCE) {
-        const float x = rnd<T>(fmaxf(v[j], a.eps_sq));
-        const float gg = rnd<T>(__fmul_rn(g[j], g[j]));
-        part += rnd<T>(__fdiv_rn(gg, x));
-      }
-    }
-    Pack<T, N>::store(p[1] + i, m);
-    Pack<T, N>::store(p[2] + i, v);
-    if (REDUCE) acc += (double)part;
-  };
-
-  if (aligned) {
-    const int nvec = s.len / V;
-#pragma unroll 2
-    for (int i = threadIdx.x; i < nvec; i += kThreads) body(std::integral_constant<int, V>{}, i * V);
-    for (int i = nvec * V + threadIdx.x; i < s.len; i += kThreads) body(std::integral_constant<int, 1>{}, i);
-  } else {
-    for (int i = threadIdx.x; i < s.len; i += kThreads) body(std::integral_constant<int, 1>{}, i);
-  }
-
-  if (REDUCE) {
-    __shared__ double warp_sum[kThreads / 32];
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, o);
+  if ((threadIdx.x & 31) == 0) warp_sum[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double t = 0.0;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, o);
-    if ((threadIdx.x & 31) == 0) warp_sum[threadIdx.x >> 5] = acc;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      double t = 0.0;
-#pragma unroll
-      for (int w = 0; w < kThreads / 32; w++) t += warp_sum[w];
-      partial[tab.chunk_base + blockIdx.x] = t;
-    }
+    for (int w = 0; w < kThreads / 32; w++) t += warp_sum[w];
+    partial[tab.tile_base + blockIdx.x] = t;
   }
 }
 
@@ -224,18 +173,18 @@ struct StableFinalizeArgs {
   int decouple_lr;
 };
 
-// One block per tensor: folds the tensor's chunk partials in a fixed order, then does on the device
+// One block per tensor: folds the tensor's tile partials in a fixed order, then does on the device
 // what the reference does on the host after `.item()` (optimi/stableadamw.py:512-524): mean and
 // square root rounded to the storage type, -lr / max(1, rms) and the weight-decay factor in double.
 template <typename T>
-__global__ void __launch_bounds__(256) stable_finalize_kernel(const __grid_constant__ MtaTable<3> tab,
+__global__ void __launch_bounds__(256) stable_finalize_kernel(const __grid_constant__ MtaTable<4> tab,
                                                               const __grid_constant__ StableFinalizeArgs a,
                                                               const double* __restrict__ partial,
                                                               float2* __restrict__ tensor_scalars) {
   const int t = blockIdx.x;
-  const int c0 = tab.chunk_start[t], c1 = tab.chunk_start[t + 1];
+  const int c0 = tab.tile_start[t], c1 = tab.tile_start[t + 1];
   double acc = 0.0;
-  for (int c = c0 + threadIdx.x; c < c1; c += 256) acc += partial[tab.chunk_base + c];
+  for (int c = c0 + threadIdx.x; c < c1; c += 256) acc += partial[tab.tile_base + c];
   __shared__ double warp_sum[8];
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, o);
@@ -257,31 +206,11 @@ __global__ void __launch_bounds__(256) stable_finalize_kernel(const __grid_const
   }
 }
 
-// Pass B.  lists: 0 p, 1 m, 2 v, 3 k.
-template <typename T, bool KAHAN>
-__global__ void __launch_bounds__(kThreads) stable_update_kernel(const __grid_constant__ MtaTable<4> tab,
-                                                                 const __grid_constant__ StableUpdateArgs a,
-                                                                 const float2* __restrict__ tensor_scalars) {
-  constexpr int V = VecN<T>::N;
-  const Span s = locate(tab, blockIdx.x);
-  T* p[4];
-  const bool aligned = chunk_pointers<T, 4>(tab, s, p);
-  const float2 sc = tensor_scalars[tab.tensor_base + s.tensor];
-  if (aligned) {
-    const int nvec = s.len / V;
-#pragma unroll 2
-    for (int i = threadIdx.x; i < nvec; i += kThreads) stable_update_run<T, KAHAN, V>(p, i * V, a, sc.x, sc.y);
-    for (int i = nvec * V + threadIdx.x; i < s.len; i += kThreads) stable_update_run<T, KAHAN, 1>(p, i, a, sc.x, sc.y);
-  } else {
-    for (int i = threadIdx.x; i < s.len; i += kThreads) stable_update_run<T, KAHAN, 1>(p, i, a, sc.x, sc.y);
-  }
-}
-
 static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
-static long long count_chunks(int n, const int64_t* numels, int chunk) {
+static long long count_tiles(int n, const int64_t* numels, int tile) {
   long long c = 0;
-  for (int i = 0; i < n; i++) c += (numels[i] + chunk - 1) / chunk;
+  for (int i = 0; i < n; i++) c += (numels[i] + tile - 1) / tile;
   return c;
 }
 
@@ -296,7 +225,6 @@ static int stableadamw_typed(int n, void* const* params, void* const* grads, voi
                              void* const* kahan_comps, const int64_t* numels, double lr, double beta1_comp, double beta2_hat,
                              double beta2_comp, double weight_decay, double eps, int decouple_lr, double max_lr, bool kahan,
                              bool update, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
-  const int chunk = pick_chunk(total_elements(n, numels));
   StableMomentsArgs ma;
   ma.l1 = make_lerp(beta1_comp);
   ma.beta2_hat = (float)beta2_hat;
@@ -304,16 +232,12 @@ static int stableadamw_typed(int n, void* const* params, void* const* grads, voi
   // the reference keeps eps^2 as a 0-dim tensor of the storage type (optimi/stableadamw.py:119)
   ma.eps_sq = round_to_storage<T>(eps * eps);
 
-  void* const* const lists_a[3] = {grads, exp_avgs, exp_avg_sqs};
-  if (!update) {
-    return for_each_table<3>(n, numels, lists_a, chunk, [&](const MtaTable<3>& tab, int chunks) {
-      stable_moments_kernel<T, false><<<chunks, kThreads, 0, stream>>>(tab, ma, nullptr);
-      return check_launch("optimi_b200_stableadamw (moments)");
-    });
-  }
+  void* const* const lists_a[4] = {grads, exp_avgs, exp_avg_sqs, nullptr};
+  if (!update) return launch_op<T, StableMomentsOp<false>>("optimi_b200_stableadamw (moments)", n, numels, lists_a, ma, stream);
 
+  constexpr int tile_a = tile_of<T, StableMomentsOp<true>>();
   const size_t scal_bytes = align_up((size_t)n * sizeof(float2), 16);
-  const size_t need = scal_bytes + (size_t)count_chunks(n, numels, chunk) * sizeof(double);
+  const size_t need = scal_bytes + (size_t)count_tiles(n, numels, tile_a) * sizeof(double);
   if (!workspace || workspace_bytes < need)
     return fail(OPTIMI_ERR_WORKSPACE_TOO_SMALL, "optimi_b200_stableadamw: workspace of %zu bytes given, %zu needed",
                 workspace ? workspace_bytes : (size_t)0, need);
@@ -328,8 +252,8 @@ static int stableadamw_typed(int n, void* const* params, void* const* grads, voi
   fa.max_lr = max_lr;
   fa.decouple_lr = decouple_lr;
 
-  int rc = for_each_table<3>(n, numels, lists_a, chunk, [&](const MtaTable<3>& tab, int chunks) {
-    stable_moments_kernel<T, true><<<chunks, kThreads, 0, stream>>>(tab, ma, partial);
+  int rc = for_each_table<4>(n, numels, lists_a, tile_a, [&](const MtaTable<4>& tab, int tiles) {
+    stable_moments_sum_kernel<T><<<tiles, kThreads, 0, stream>>>(tab, ma, partial);
     int r = check_launch("optimi_b200_stableadamw (moments)");
     if (r != OPTIMI_OK) return r;
     stable_finalize_kernel<T><<<tab.n_tensors, 256, 0, stream>>>(tab, fa, partial, tensor_scalars);
@@ -338,14 +262,12 @@ static int stableadamw_typed(int n, void* const* params, void* const* grads, voi
   if (rc != OPTIMI_OK) return rc;
 
   StableUpdateArgs ua;
+  ua.tensor_scalars = tensor_scalars;
   ua.eps = (float)eps;
   ua.has_wd = weight_decay != 0;
   void* const* const lists_b[4] = {params, exp_avgs, exp_avg_sqs, kahan ? kahan_comps : nullptr};
-  return for_each_table<4>(n, numels, lists_b, chunk, [&](const MtaTable<4>& tab, int chunks) {
-    if (kahan) stable_update_kernel<T, true><<<chunks, kThreads, 0, stream>>>(tab, ua, tensor_scalars);
-    else stable_update_kernel<T, false><<<chunks, kThreads, 0, stream>>>(tab, ua, tensor_scalars);
-    return check_launch("optimi_b200_stableadamw (update)");
-  });
+  if (kahan) return launch_op<T, StableUpdateOp<true>>("optimi_b200_stableadamw (update)", n, numels, lists_b, ua, stream);
+  return launch_op<T, StableUpdateOp<false>>("optimi_b200_stableadamw (update)", n, numels, lists_b, ua, stream);
 }
 
 static int wd_mode_of(double weight_decay, int decouple_wd) {
@@ -364,6 +286,8 @@ extern "C" {
 const char* optimi_b200_last_error(void) { return g_error; }
 
 int optimi_b200_version(void) { return 100; }
+
+unsigned long long optimi_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 int optimi_b200_adam(int n, void* const* params, void* const* grads, void* const* exp_avgs, void* const* exp_avg_sqs,
                      void* const* kahan_comps, const int64_t* numels, int dtype, double lr, double beta1_comp,
@@ -497,8 +421,9 @@ int optimi_b200_adan(int n, void* const* params, void* const* grads, void* const
 
 size_t optimi_b200_stableadamw_workspace_bytes(int n, const int64_t* numels) {
   if (n <= 0 || !numels) return 16;
-  const int chunk = pick_chunk(total_elements(n, numels));
-  return align_up((size_t)n * sizeof(float2), 16) + (size_t)count_chunks(n, numels, chunk) * sizeof(double) + 16;
+  // the float32 tile is the smallest, so this bounds every storage type
+  constexpr int tile = tile_of<float, StableMomentsOp<true>>();
+  return align_up((size_t)n * sizeof(float2), 16) + (size_t)count_tiles(n, numels, tile) * sizeof(double) + 16;
 }
 
 int optimi_b200_stableadamw(int n, void* const* params, void* const* grads, void* const* exp_avgs, void* const* exp_avg_sqs,

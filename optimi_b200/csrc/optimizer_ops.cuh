@@ -1,19 +1,30 @@
-// Per-element arithmetic of the eight optimizers, as "ops" for mta_kernel.
+// Per-element arithmetic of the eight optimizers, as "ops" for the generic multi-tensor kernel.
 //
-// Every op replays the reference's foreach sequence for its optimizer in registers: each line that
-// ends in rnd<T>(...) is ONE ATen op of that sequence — an fp32 computation followed by a rounding
-// to the storage type — in the reference's order, with the fp32 formula the CUDA build of that
-// ATen op uses (fused multiply-add for `x + s*y`, correctly rounded sqrt and divide, division by
-// a scalar as multiplication by its reciprocal).  Intermediates that the reference keeps in the
+// Every op replays the reference's foreach sequence for its optimizer in registers: each statement
+// that ends in rnd<T>(...) is ONE ATen op of that sequence — an fp32 computation followed by a
+// rounding to the storage type — in the reference's order, with the fp32 formula the CUDA build of
+// that ATen op uses (fused multiply-add for `x + s*y`, correctly rounded sqrt and divide, division
+// by a scalar as multiplication by its reciprocal).  Intermediates that the reference keeps in the
 // gradient buffer live in registers here, so gradients are never written.
 //
-// Template flags: KAHAN = Kahan-compensated update (low-precision storage only), UPDATE = false is
-// the optimizer-accumulation micro-step (state averages only).
+// Template flags: KAHAN = Kahan-compensated update (16-bit storage only), UPDATE = false is the
+// optimizer-accumulation micro-step (state averages only).
 #pragma once
 
 #include "mta_common.cuh"
 
 namespace optimi {
+
+// vectors per thread per stream in a full tile (tuning knobs; the defaults are the measured best)
+#ifndef OPTIMI_U_ADAM
+#define OPTIMI_U_ADAM 1
+#endif
+#ifndef OPTIMI_U_NARROW
+#define OPTIMI_U_NARROW 1
+#endif
+#ifndef OPTIMI_U_WIDE
+#define OPTIMI_U_WIDE 1
+#endif
 
 enum WdMode : int { kWdNone = 0, kWdDecoupled = 1, kWdL2 = 2 };
 
@@ -29,8 +40,7 @@ __device__ __forceinline__ void kahan_tail(float& p, float& k) {
 // copy ; sqrt ; add eps                                  (e.g. optimi/adam.py:437-439)
 template <typename T>
 __device__ __forceinline__ float denominator(float v, float eps) {
-  const float d = rnd<T>(__fsqrt_rn(v));
-  return rnd<T>(__fadd_rn(d, eps));
+  return rnd<T>(__fadd_rn(sqrt_rnd<T>(v), eps));
 }
 
 // addcdiv: x + value * (a / b)
@@ -38,13 +48,29 @@ __device__ __forceinline__ float addcdiv_op(float x, float a, float b, float val
   return __fmaf_rn(value, __fdiv_rn(a, b), x);
 }
 
-struct Lerp {  // uniform pieces of one scalar-weight lerp
-  float w, omw;
-  int low;
+// lerp ; mul ; addcmul                                    (e.g. optimi/adam.py:431-434)
+template <typename T>
+__device__ __forceinline__ void adam_moments(float& m, float& v, float g, const Lerp& l1, float beta2_hat, float beta2_comp) {
+  m = rnd<T>(lerp_op(m, g, l1));
+  v = rnd<T>(__fmul_rn(v, beta2_hat));
+  v = rnd<T>(__fmaf_rn(beta2_comp, __fmul_rn(g, g), v));
+}
+
+template <typename T>
+__device__ __forceinline__ void weight_decay(float& p, float& g, int mode, float wd) {
+  if (mode == kWdDecoupled) p = rnd<T>(__fmul_rn(p, wd));
+  else if (mode == kWdL2) g = rnd<T>(__fmaf_rn(wd, p, g));
+}
+
+struct OpBase {
+  using Ctx = NoCtx;
+  static constexpr int kSumSlot = -1;
+  template <class Table, class Args>
+  static __device__ __forceinline__ NoCtx context(const Table&, const Span&, const Args&) { return NoCtx{}; }
 };
 
 // ---------------------------------------------------------------------------------------------
-// Adam / AdamW                       lists: 0 p, 1 g, 2 m (exp_avg), 3 v (exp_avg_sq), 4 k (kahan)
+// Adam / AdamW                                       lists: 0 p, 1 g, 2 m, 3 v, 4 k (kahan)
 // optimi/adam.py:424-453
 // ---------------------------------------------------------------------------------------------
 struct AdamArgs {
@@ -53,52 +79,31 @@ struct AdamArgs {
   int wd_mode;
 };
 
-template <typename T>
-__device__ __forceinline__ void adam_moments(float& m, float& v, float g, const Lerp& l1, float beta2_hat,
-                                             float beta2_comp) {
-  m = rnd<T>(lerp_op(m, g, l1.w, l1.omw, l1.low));
-  v = rnd<T>(__fmul_rn(v, beta2_hat));
-  v = rnd<T>(__fmaf_rn(beta2_comp, __fmul_rn(g, g), v));
-}
-
 template <bool KAHAN, bool UPDATE>
-struct AdamOp {
-  static constexpr int NL = 5;
+struct AdamOp : OpBase {
+  static constexpr int NL = 5, U = OPTIMI_U_ADAM;
   using Args = AdamArgs;
-  template <typename T, int N>
-  static __device__ __forceinline__ void run(T* const (&ptr)[NL], int i, const Args& a) {
-    float p[N], g[N], m[N], v[N], k[N];
-    Pack<T, N>::load(ptr[1] + i, g);
-    Pack<T, N>::load(ptr[2] + i, m);
-    Pack<T, N>::load(ptr[3] + i, v);
-    if (UPDATE) Pack<T, N>::load(ptr[0] + i, p);
-    if (KAHAN) Pack<T, N>::load(ptr[4] + i, k);
-#pragma unroll
-    for (int j = 0; j < N; j++) {
-      if (UPDATE) {
-        if (a.wd_mode == kWdDecoupled) p[j] = rnd<T>(__fmul_rn(p[j], a.wd));
-        else if (a.wd_mode == kWdL2) g[j] = rnd<T>(__fmaf_rn(a.wd, p[j], g[j]));
-      }
-      adam_moments<T>(m[j], v[j], g[j], a.l1, a.beta2_hat, a.beta2_comp);
-      if (UPDATE) {
-        const float den = denominator<T>(v[j], a.eps);
-        if (KAHAN) {
-          k[j] = rnd<T>(addcdiv_op(k[j], m[j], den, a.neg_lr));
-          kahan_tail<T>(p[j], k[j]);
-        } else {
-          p[j] = rnd<T>(addcdiv_op(p[j], m[j], den, a.neg_lr));
-        }
+  static __device__ __forceinline__ bool reads(int l, const Args&) { return l == 0 ? UPDATE : l == 4 ? KAHAN : true; }
+  static __device__ __forceinline__ bool writes(int l, const Args&) { return l == 0 ? UPDATE : l == 4 ? KAHAN : l != 1; }
+  template <typename T>
+  static __device__ __forceinline__ void elem(float (&e)[NL], const Args& a, const NoCtx&) {
+    float &p = e[0], &g = e[1], &m = e[2], &v = e[3], &k = e[4];
+    if (UPDATE) weight_decay<T>(p, g, a.wd_mode, a.wd);
+    adam_moments<T>(m, v, g, a.l1, a.beta2_hat, a.beta2_comp);
+    if (UPDATE) {
+      const float den = denominator<T>(v, a.eps);
+      if (KAHAN) {
+        k = rnd<T>(addcdiv_op(k, m, den, a.neg_lr));
+        kahan_tail<T>(p, k);
+      } else {
+        p = rnd<T>(addcdiv_op(p, m, den, a.neg_lr));
       }
     }
-    Pack<T, N>::store(ptr[2] + i, m);
-    Pack<T, N>::store(ptr[3] + i, v);
-    if (UPDATE) Pack<T, N>::store(ptr[0] + i, p);
-    if (KAHAN) Pack<T, N>::store(ptr[4] + i, k);
   }
 };
 
 // ---------------------------------------------------------------------------------------------
-// RAdam and Ranger          lists: 0 p, 1 g, 2 m, 3 v, 4 k, 5 la (slow weights, Ranger only)
+// RAdam and Ranger              lists: 0 p, 1 g, 2 m, 3 v, 4 k, 5 la (slow weights, Ranger only)
 // optimi/radam.py:438-479, optimi/ranger.py:498-561
 // ---------------------------------------------------------------------------------------------
 struct RangerArgs {
@@ -109,54 +114,40 @@ struct RangerArgs {
 };
 
 template <bool KAHAN, bool UPDATE>
-struct RangerOp {
-  static constexpr int NL = 6;
+struct RangerOp : OpBase {
+  static constexpr int NL = 6, U = OPTIMI_U_ADAM;
   using Args = RangerArgs;
-  template <typename T, int N>
-  static __device__ __forceinline__ void run(T* const (&ptr)[NL], int i, const Args& a) {
-    float p[N], g[N], m[N], v[N], k[N], la[N];
-    const bool look = UPDATE && a.lookahead;
-    Pack<T, N>::load(ptr[1] + i, g);
-    Pack<T, N>::load(ptr[2] + i, m);
-    Pack<T, N>::load(ptr[3] + i, v);
-    if (UPDATE) Pack<T, N>::load(ptr[0] + i, p);
-    if (KAHAN) Pack<T, N>::load(ptr[4] + i, k);
-    if (look) Pack<T, N>::load(ptr[5] + i, la);
-#pragma unroll
-    for (int j = 0; j < N; j++) {
-      if (UPDATE) {
-        if (a.wd_mode == kWdDecoupled) p[j] = rnd<T>(__fmul_rn(p[j], a.wd));
-        else if (a.wd_mode == kWdL2) g[j] = rnd<T>(__fmaf_rn(a.wd, p[j], g[j]));
-      }
-      adam_moments<T>(m[j], v[j], g[j], a.l1, a.beta2_hat, a.beta2_comp);
-      if (UPDATE) {
-        float x = KAHAN ? k[j] : p[j];
-        if (a.use_rect) x = rnd<T>(addcdiv_op(x, m[j], denominator<T>(v[j], a.eps), a.neg_lr));
-        else x = rnd<T>(__fmaf_rn(a.neg_lr, m[j], x));
-        if (KAHAN) {
-          k[j] = x;
-          kahan_tail<T>(p[j], k[j]);
-          if (look) {  // optimi/ranger.py:537-549
-            const float diff = rnd<T>(__fsub_rn(p[j], la[j]));
-            k[j] = rnd<T>(__fmaf_rn(a.alpha, diff, k[j]));
-            kahan_tail<T>(la[j], k[j]);
-            p[j] = la[j];
-          }
-        } else {
-          p[j] = x;
-          if (look) {  // optimi/ranger.py:559-561
-            p[j] = rnd<T>(__fsub_rn(p[j], la[j]));
-            la[j] = rnd<T>(__fmaf_rn(a.alpha, p[j], la[j]));
-            p[j] = la[j];
-          }
+  static __device__ __forceinline__ bool reads(int l, const Args& a) {
+    return l == 0 ? UPDATE : l == 4 ? KAHAN : l == 5 ? (UPDATE && a.lookahead) : true;
+  }
+  static __device__ __forceinline__ bool writes(int l, const Args& a) { return l != 1 && reads(l, a); }
+  template <typename T>
+  static __device__ __forceinline__ void elem(float (&e)[NL], const Args& a, const NoCtx&) {
+    float &p = e[0], &g = e[1], &m = e[2], &v = e[3], &k = e[4], &la = e[5];
+    if (UPDATE) weight_decay<T>(p, g, a.wd_mode, a.wd);
+    adam_moments<T>(m, v, g, a.l1, a.beta2_hat, a.beta2_comp);
+    if (UPDATE) {
+      float x = KAHAN ? k : p;
+      if (a.use_rect) x = rnd<T>(addcdiv_op(x, m, denominator<T>(v, a.eps), a.neg_lr));
+      else x = rnd<T>(__fmaf_rn(a.neg_lr, m, x));
+      if (KAHAN) {
+        k = x;
+        kahan_tail<T>(p, k);
+        if (a.lookahead) {  // optimi/ranger.py:537-549
+          const float diff = rnd<T>(__fsub_rn(p, la));
+          k = rnd<T>(__fmaf_rn(a.alpha, diff, k));
+          kahan_tail<T>(la, k);
+          p = la;
+        }
+      } else {
+        p = x;
+        if (a.lookahead) {  // optimi/ranger.py:559-561
+          p = rnd<T>(__fsub_rn(p, la));
+          la = rnd<T>(__fmaf_rn(a.alpha, p, la));
+          p = la;
         }
       }
     }
-    Pack<T, N>::store(ptr[2] + i, m);
-    Pack<T, N>::store(ptr[3] + i, v);
-    if (UPDATE) Pack<T, N>::store(ptr[0] + i, p);
-    if (KAHAN) Pack<T, N>::store(ptr[4] + i, k);
-    if (look) Pack<T, N>::store(ptr[5] + i, la);
   }
 };
 
@@ -171,37 +162,29 @@ struct LionArgs {
 };
 
 template <bool KAHAN, bool UPDATE>
-struct LionOp {
-  static constexpr int NL = 4;
+struct LionOp : OpBase {
+  static constexpr int NL = 4, U = OPTIMI_U_NARROW;
   using Args = LionArgs;
-  template <typename T, int N>
-  static __device__ __forceinline__ void run(T* const (&ptr)[NL], int i, const Args& a) {
-    float p[N], g[N], m[N], k[N];
-    Pack<T, N>::load(ptr[1] + i, g);
-    Pack<T, N>::load(ptr[2] + i, m);
-    if (UPDATE) Pack<T, N>::load(ptr[0] + i, p);
-    if (KAHAN) Pack<T, N>::load(ptr[3] + i, k);
-#pragma unroll
-    for (int j = 0; j < N; j++) {
-      float u = 0.f;
-      if (UPDATE) {
-        if (a.wd_mode == kWdDecoupled) p[j] = rnd<T>(__fmul_rn(p[j], a.wd));
-        u = rnd<T>(lerp_op(m[j], g[j], a.l1.w, a.l1.omw, a.l1.low));
-        u = (float)((0.f < u) - (u < 0.f));
-      }
-      m[j] = rnd<T>(lerp_op(m[j], g[j], a.l2.w, a.l2.omw, a.l2.low));
-      if (UPDATE) {
-        if (KAHAN) {
-          k[j] = rnd<T>(__fmaf_rn(a.neg_lr, u, k[j]));
-          kahan_tail<T>(p[j], k[j]);
-        } else {
-          p[j] = rnd<T>(__fmaf_rn(a.neg_lr, u, p[j]));
-        }
+  static __device__ __forceinline__ bool reads(int l, const Args&) { return l == 0 ? UPDATE : l == 3 ? KAHAN : true; }
+  static __device__ __forceinline__ bool writes(int l, const Args& a) { return l != 1 && reads(l, a); }
+  template <typename T>
+  static __device__ __forceinline__ void elem(float (&e)[NL], const Args& a, const NoCtx&) {
+    float &p = e[0], &g = e[1], &m = e[2], &k = e[3];
+    float u = 0.f;
+    if (UPDATE) {
+      if (a.wd_mode == kWdDecoupled) p = rnd<T>(__fmul_rn(p, a.wd));
+      u = rnd<T>(lerp_op(m, g, a.l1));
+      u = (float)((0.f < u) - (u < 0.f));
+    }
+    m = rnd<T>(lerp_op(m, g, a.l2));
+    if (UPDATE) {
+      if (KAHAN) {
+        k = rnd<T>(__fmaf_rn(a.neg_lr, u, k));
+        kahan_tail<T>(p, k);
+      } else {
+        p = rnd<T>(__fmaf_rn(a.neg_lr, u, p));
       }
     }
-    Pack<T, N>::store(ptr[2] + i, m);
-    if (UPDATE) Pack<T, N>::store(ptr[0] + i, p);
-    if (KAHAN) Pack<T, N>::store(ptr[3] + i, k);
   }
 };
 
@@ -216,44 +199,35 @@ struct SgdArgs {
 };
 
 template <bool KAHAN, bool UPDATE>
-struct SgdOp {
-  static constexpr int NL = 4;
+struct SgdOp : OpBase {
+  static constexpr int NL = 4, U = OPTIMI_U_NARROW;
   using Args = SgdArgs;
-  template <typename T, int N>
-  static __device__ __forceinline__ void run(T* const (&ptr)[NL], int i, const Args& a) {
-    float p[N], g[N], m[N], k[N];
-    Pack<T, N>::load(ptr[1] + i, g);
-    if (a.has_momentum) Pack<T, N>::load(ptr[2] + i, m);
-    if (UPDATE) Pack<T, N>::load(ptr[0] + i, p);
-    if (KAHAN) Pack<T, N>::load(ptr[3] + i, k);
-#pragma unroll
-    for (int j = 0; j < N; j++) {
-      if (UPDATE) {
-        if (a.wd_mode == kWdDecoupled) p[j] = rnd<T>(__fmul_rn(p[j], a.wd));
-        else if (a.wd_mode == kWdL2) g[j] = rnd<T>(__fmaf_rn(a.wd, p[j], g[j]));
+  static __device__ __forceinline__ bool reads(int l, const Args& a) {
+    return l == 0 ? UPDATE : l == 2 ? a.has_momentum != 0 : l == 3 ? KAHAN : true;
+  }
+  static __device__ __forceinline__ bool writes(int l, const Args& a) { return l != 1 && reads(l, a); }
+  template <typename T>
+  static __device__ __forceinline__ void elem(float (&e)[NL], const Args& a, const NoCtx&) {
+    float &p = e[0], &g = e[1], &m = e[2], &k = e[3];
+    if (UPDATE) weight_decay<T>(p, g, a.wd_mode, a.wd);
+    float upd = g;
+    if (a.has_momentum) {
+      if (a.dampening) {
+        m = rnd<T>(lerp_op(m, g, a.damp));
+      } else {
+        m = rnd<T>(__fmul_rn(m, a.momentum));
+        m = rnd<T>(__fadd_rn(m, g));
       }
-      float upd = g[j];
-      if (a.has_momentum) {
-        if (a.dampening) {
-          m[j] = rnd<T>(lerp_op(m[j], g[j], a.damp.w, a.damp.omw, a.damp.low));
-        } else {
-          m[j] = rnd<T>(__fmul_rn(m[j], a.momentum));
-          m[j] = rnd<T>(__fadd_rn(m[j], g[j]));
-        }
-        upd = m[j];
-      }
-      if (UPDATE) {
-        if (KAHAN) {
-          k[j] = rnd<T>(__fmaf_rn(a.neg_lr, upd, k[j]));
-          kahan_tail<T>(p[j], k[j]);
-        } else {
-          p[j] = rnd<T>(__fmaf_rn(a.neg_lr, upd, p[j]));
-        }
+      upd = m;
+    }
+    if (UPDATE) {
+      if (KAHAN) {
+        k = rnd<T>(__fmaf_rn(a.neg_lr, upd, k));
+        kahan_tail<T>(p, k);
+      } else {
+        p = rnd<T>(__fmaf_rn(a.neg_lr, upd, p));
       }
     }
-    if (a.has_momentum) Pack<T, N>::store(ptr[2] + i, m);
-    if (UPDATE) Pack<T, N>::store(ptr[0] + i, p);
-    if (KAHAN) Pack<T, N>::store(ptr[3] + i, k);
   }
 };
 
@@ -269,49 +243,63 @@ struct AdanArgs {
 };
 
 template <bool KAHAN, bool UPDATE>
-struct AdanOp {
-  static constexpr int NL = 7;
+struct AdanOp : OpBase {
+  static constexpr int NL = 7, U = OPTIMI_U_WIDE;
   using Args = AdanArgs;
-  template <typename T, int N>
-  static __device__ __forceinline__ void run(T* const (&ptr)[NL], int i, const Args& a) {
-    float p[N], g[N], m[N], d[N], q[N], pg[N], k[N];
-    Pack<T, N>::load(ptr[1] + i, g);
-    Pack<T, N>::load(ptr[2] + i, m);
-    Pack<T, N>::load(ptr[3] + i, d);
-    Pack<T, N>::load(ptr[4] + i, q);
-    Pack<T, N>::load(ptr[5] + i, pg);
-    if (UPDATE) Pack<T, N>::load(ptr[0] + i, p);
-    if (KAHAN) Pack<T, N>::load(ptr[6] + i, k);
-#pragma unroll
-    for (int j = 0; j < N; j++) {
-      float diff = rnd<T>(__fadd_rn(pg[j], g[j]));
-      m[j] = rnd<T>(lerp_op(m[j], g[j], a.l1.w, a.l1.omw, a.l1.low));
-      d[j] = rnd<T>(lerp_op(d[j], diff, a.l2.w, a.l2.omw, a.l2.low));
-      diff = rnd<T>(__fmul_rn(diff, a.beta2));
-      diff = rnd<T>(__fadd_rn(diff, g[j]));
-      q[j] = rnd<T>(__fmul_rn(q[j], a.beta3_hat));
-      q[j] = rnd<T>(__fmaf_rn(a.beta3_comp, __fmul_rn(diff, diff), q[j]));
-      pg[j] = -g[j];
-      if (UPDATE) {
-        const float den = denominator<T>(q[j], a.eps);
-        if (a.wd_mode == 1) p[j] = rnd<T>(__fmul_rn(p[j], a.wd_mul));
-        if (KAHAN) {
-          k[j] = rnd<T>(addcdiv_op(k[j], m[j], den, a.neg_lr));
-          k[j] = rnd<T>(addcdiv_op(k[j], d[j], den, a.neg_lr_beta2));
-          kahan_tail<T>(p[j], k[j]);
-        } else {
-          p[j] = rnd<T>(addcdiv_op(p[j], m[j], den, a.neg_lr));
-          p[j] = rnd<T>(addcdiv_op(p[j], d[j], den, a.neg_lr_beta2));
-        }
-        if (a.wd_mode == 2) p[j] = rnd<T>(__fmul_rn(p[j], a.wd_mul));
+  static __device__ __forceinline__ bool reads(int l, const Args&) { return l == 0 ? UPDATE : l == 6 ? KAHAN : true; }
+  static __device__ __forceinline__ bool writes(int l, const Args& a) { return l != 1 && reads(l, a); }
+  template <typename T>
+  static __device__ __forceinline__ void elem(float (&e)[NL], const Args& a, const NoCtx&) {
+    float &p = e[0], &g = e[1], &m = e[2], &d = e[3], &q = e[4], &pg = e[5], &k = e[6];
+    float diff = rnd<T>(__fadd_rn(pg, g));
+    m = rnd<T>(lerp_op(m, g, a.l1));
+    d = rnd<T>(lerp_op(d, diff, a.l2));
+    diff = rnd<T>(__fmul_rn(diff, a.beta2));
+    diff = rnd<T>(__fadd_rn(diff, g));
+    q = rnd<T>(__fmul_rn(q, a.beta3_hat));
+    q = rnd<T>(__fmaf_rn(a.beta3_comp, __fmul_rn(diff, diff), q));
+    pg = -g;
+    if (UPDATE) {
+      const float den = denominator<T>(q, a.eps);
+      if (a.wd_mode == 1) p = rnd<T>(__fmul_rn(p, a.wd_mul));
+      if (KAHAN) {
+        k = rnd<T>(addcdiv_op(k, m, den, a.neg_lr));
+        k = rnd<T>(addcdiv_op(k, d, den, a.neg_lr_beta2));
+        kahan_tail<T>(p, k);
+      } else {
+        p = rnd<T>(addcdiv_op(p, m, den, a.neg_lr));
+        p = rnd<T>(addcdiv_op(p, d, den, a.neg_lr_beta2));
       }
+      if (a.wd_mode == 2) p = rnd<T>(__fmul_rn(p, a.wd_mul));
     }
-    Pack<T, N>::store(ptr[2] + i, m);
-    Pack<T, N>::store(ptr[3] + i, d);
-    Pack<T, N>::store(ptr[4] + i, q);
-    Pack<T, N>::store(ptr[5] + i, pg);
-    if (UPDATE) Pack<T, N>::store(ptr[0] + i, p);
-    if (KAHAN) Pack<T, N>::store(ptr[6] + i, k);
+  }
+};
+
+// ---------------------------------------------------------------------------------------------
+// StableAdamW, pass A (moments + per-tile sum)       lists: 0 g, 1 m, 2 v, 3 r (pseudo, no memory)
+// optimi/stableadamw.py:499-506.  e[3] carries g^2 / max(v, eps^2) out for the tile sum.
+// ---------------------------------------------------------------------------------------------
+struct StableMomentsArgs {
+  Lerp l1;
+  float beta2_hat, beta2_comp, eps_sq;  // eps_sq: eps^2 rounded to the storage type
+};
+
+template <bool REDUCE>
+struct StableMomentsOp : OpBase {
+  static constexpr int NL = 4, U = OPTIMI_U_NARROW;
+  static constexpr int kSumSlot = REDUCE ? 3 : -1;
+  using Args = StableMomentsArgs;
+  static __device__ __forceinline__ bool reads(int l, const Args&) { return l != 3; }
+  static __device__ __forceinline__ bool writes(int l, const Args&) { return l == 1 || l == 2; }
+  template <typename T>
+  static __device__ __forceinline__ void elem(float (&e)[NL], const Args& a, const NoCtx&) {
+    float &g = e[0], &m = e[1], &v = e[2];
+    adam_moments<T>(m, v, g, a.l1, a.beta2_hat, a.beta2_comp);
+    if (REDUCE) {
+      const float x = rnd<T>(fmaxf(v, a.eps_sq));
+      const float gg = rnd<T>(__fmul_rn(g, g));
+      e[3] = rnd<T>(__fdiv_rn(gg, x));
+    }
   }
 };
 
@@ -320,31 +308,35 @@ struct AdanOp {
 // optimi/stableadamw.py:522-544.  The clipped -lr and the weight-decay factor are per tensor.
 // ---------------------------------------------------------------------------------------------
 struct StableUpdateArgs {
+  const float2* tensor_scalars;  // per tensor: x = -lr / max(1, rms), y = weight-decay factor
   float eps;
   int has_wd;
 };
 
-template <typename T, bool KAHAN, int N>
-__device__ __forceinline__ void stable_update_run(T* const (&ptr)[4], int i, const StableUpdateArgs& a, float neg_lr,
-                                                  float wd) {
-  float p[N], m[N], v[N], k[N];
-  Pack<T, N>::load(ptr[0] + i, p);
-  Pack<T, N>::load(ptr[1] + i, m);
-  Pack<T, N>::load(ptr[2] + i, v);
-  if (KAHAN) Pack<T, N>::load(ptr[3] + i, k);
-#pragma unroll
-  for (int j = 0; j < N; j++) {
-    if (a.has_wd) p[j] = rnd<T>(__fmul_rn(p[j], wd));
-    const float den = denominator<T>(v[j], a.eps);
+template <bool KAHAN>
+struct StableUpdateOp {
+  static constexpr int NL = 4, U = OPTIMI_U_NARROW;
+  static constexpr int kSumSlot = -1;
+  using Args = StableUpdateArgs;
+  using Ctx = float2;
+  template <class Table>
+  static __device__ __forceinline__ float2 context(const Table& tab, const Span& s, const Args& a) {
+    return a.tensor_scalars[tab.tensor_base + s.tensor];
+  }
+  static __device__ __forceinline__ bool reads(int l, const Args&) { return l == 3 ? KAHAN : true; }
+  static __device__ __forceinline__ bool writes(int l, const Args&) { return l == 0 || (l == 3 && KAHAN); }
+  template <typename T>
+  static __device__ __forceinline__ void elem(float (&e)[NL], const Args& a, const float2& sc) {
+    float &p = e[0], &m = e[1], &v = e[2], &k = e[3];
+    if (a.has_wd) p = rnd<T>(__fmul_rn(p, sc.y));
+    const float den = denominator<T>(v, a.eps);
     if (KAHAN) {
-      k[j] = rnd<T>(addcdiv_op(k[j], m[j], den, neg_lr));
-      kahan_tail<T>(p[j], k[j]);
+      k = rnd<T>(addcdiv_op(k, m, den, sc.x));
+      kahan_tail<T>(p, k);
     } else {
-      p[j] = rnd<T>(addcdiv_op(p[j], m[j], den, neg_lr));
+      p = rnd<T>(addcdiv_op(p, m, den, sc.x));
     }
   }
-  Pack<T, N>::store(ptr[0] + i, p);
-  if (KAHAN) Pack<T, N>::store(ptr[3] + i, k);
-}
+};
 
 }  // namespace optimi

@@ -85,6 +85,7 @@ def adam(
     gradient_release: bool = False,
     optimizer_accumulation: bool = False,
     _stream=None,
+    _trusted: bool = False,
 ):
     """Adam / AdamW step on lists of tensors (or bare tensors in gradient-release form)."""
     t = _advance(step)
@@ -96,7 +97,7 @@ def adam(
             int(not optimizer_accumulation))  # fmt: skip
     launch(
         "optimi_b200_adam", [params, grads, exp_avgs, exp_avg_sqs, kahan_comps],
-        ("params", "grads", "exp_avgs", "exp_avg_sqs", "kahan_comps"), lambda *_: tail, _stream,
+        ("params", "grads", "exp_avgs", "exp_avg_sqs", "kahan_comps"), lambda *_: tail, _stream, _trusted,
     )  # fmt: skip
 
 
@@ -121,12 +122,13 @@ def adamw(
     gradient_release: bool = False,
     optimizer_accumulation: bool = False,
     _stream=None,
+    _trusted: bool = False,
 ):
     """AdamW step: `adam` with decoupled weight decay (optimi/adamw.py:123-143)."""
     adam(
         params, grads, exp_avgs, exp_avg_sqs, kahan_comps, lr=lr, beta1=beta1, beta2=beta2, weight_decay=weight_decay,
         eps=eps, step=step, decouple_wd=True, decouple_lr=decouple_lr, max_lr=max_lr, kahan_sum=kahan_sum,
-        gradient_release=gradient_release, optimizer_accumulation=optimizer_accumulation, _stream=_stream,
+        gradient_release=gradient_release, optimizer_accumulation=optimizer_accumulation, _stream=_stream, _trusted=_trusted,
     )  # fmt: skip
 
 
@@ -148,12 +150,13 @@ def lion(
     gradient_release: bool = False,
     optimizer_accumulation: bool = False,
     _stream=None,
+    _trusted: bool = False,
 ):
     """Lion step.  Weight decay is always decoupled (optimi/lion.py:227-231)."""
     wd = _fold_weight_decay(weight_decay, lr, True, decouple_lr, max_lr)
     tail = (lr, 1 - beta1, 1 - beta2, wd, int(bool(kahan_sum)), int(not optimizer_accumulation))
     launch("optimi_b200_lion", [params, grads, exp_avgs, kahan_comps], ("params", "grads", "exp_avgs", "kahan_comps"),
-           lambda *_: tail, _stream)  # fmt: skip
+           lambda *_: tail, _stream, _trusted)  # fmt: skip
 
 
 def sgd(
@@ -175,6 +178,7 @@ def sgd(
     gradient_release: bool = False,
     optimizer_accumulation: bool = False,
     _stream=None,
+    _trusted: bool = False,
 ):
     """SGD step with optional momentum, dampening and (decoupled) weight decay."""
     wd = _fold_weight_decay(weight_decay, lr, decouple_wd, decouple_lr, max_lr)
@@ -183,7 +187,7 @@ def sgd(
     tail = (lr, momentum, wd, int(bool(dampening)), int(decouple_wd or decouple_lr), int(bool(kahan_sum)),
             int(not optimizer_accumulation))  # fmt: skip
     launch("optimi_b200_sgd", [params, grads, exp_avgs, kahan_comps], ("params", "grads", "exp_avgs", "kahan_comps"),
-           lambda *_: tail, _stream)  # fmt: skip
+           lambda *_: tail, _stream, _trusted)  # fmt: skip
 
 
 _workspaces: dict[tuple, Tensor] = {}
@@ -223,6 +227,7 @@ def stableadamw(
     optimizer_accumulation: bool = False,
     mean_squares: TensorList = None,
     _stream=None,
+    _trusted: bool = False,
 ):
     """StableAdamW step.  `eps_sqs` and `mean_squares` are accepted for signature compatibility; the
     kernels derive eps^2 from `eps` and keep the per-tensor mean square in their own scratch."""
@@ -247,7 +252,7 @@ def stableadamw(
 
     launch(
         "optimi_b200_stableadamw", [params, grads, exp_avgs, exp_avg_sqs, kahan_comps],
-        ("params", "grads", "exp_avgs", "exp_avg_sqs", "kahan_comps"), tail, _stream,
+        ("params", "grads", "exp_avgs", "exp_avg_sqs", "kahan_comps"), tail, _stream, _trusted,
     )  # fmt: skip
 
 
@@ -276,6 +281,7 @@ def adan(
     gradient_release: bool = False,
     optimizer_accumulation: bool = False,
     _stream=None,
+    _trusted: bool = False,
 ):
     """Adan step.  `prev_grads` holds the negated previous gradient."""
     t = _advance(step)
@@ -291,7 +297,7 @@ def adan(
             int(not optimizer_accumulation))  # fmt: skip
     launch(
         "optimi_b200_adan", [params, grads, exp_avgs, exp_avg_diffs, exp_avg_sqs, prev_grads, kahan_comps],
-        ("params", "grads", "exp_avgs", "exp_avg_diffs", "exp_avg_sqs", "prev_grads", "kahan_comps"), lambda *_: tail, _stream,
+        ("params", "grads", "exp_avgs", "exp_avg_diffs", "exp_avg_sqs", "prev_grads", "kahan_comps"), lambda *_: tail, _stream, _trusted,
     )  # fmt: skip
 
 
@@ -317,6 +323,7 @@ def radam(
     gradient_release: bool = False,
     optimizer_accumulation: bool = False,
     _stream=None,
+    _trusted: bool = False,
 ):
     """RAdam step: Adam averages with a rectified step once the variance estimate is trusted."""
     t = _advance(step)
@@ -329,7 +336,7 @@ def radam(
             int(decouple_wd or decouple_lr), int(bool(kahan_sum)), int(not optimizer_accumulation))  # fmt: skip
     launch(
         "optimi_b200_radam", [params, grads, exp_avgs, exp_avg_sqs, kahan_comps],
-        ("params", "grads", "exp_avgs", "exp_avg_sqs", "kahan_comps"), lambda *_: tail, _stream,
+        ("params", "grads", "exp_avgs", "exp_avg_sqs", "kahan_comps"), lambda *_: tail, _stream, _trusted,
     )  # fmt: skip
 
 
@@ -358,6 +365,7 @@ def ranger(
     gradient_release: bool = False,
     optimizer_accumulation: bool = False,
     _stream=None,
+    _trusted: bool = False,
 ):
     """Ranger step: RAdam followed, on every k-th step, by a Lookahead pull toward the slow weights."""
     t = _advance(step)
@@ -370,5 +378,5 @@ def ranger(
             int(t % k == 0), alpha, int(decouple_wd or decouple_lr), int(bool(kahan_sum)), int(not optimizer_accumulation))  # fmt: skip
     launch(
         "optimi_b200_ranger", [params, grads, exp_avgs, exp_avg_sqs, la_params, kahan_comps],
-        ("params", "grads", "exp_avgs", "exp_avg_sqs", "la_params", "kahan_comps"), lambda *_: tail, _stream,
+        ("params", "grads", "exp_avgs", "exp_avg_sqs", "la_params", "kahan_comps"), lambda *_: tail, _stream, _trusted,
     )  # fmt: skip

@@ -109,6 +109,8 @@ class OptimiOptimizer(Optimizer):
     def _init_state(self, group: dict[str, Any], state: dict[str, Any], param: Tensor) -> None:
         if "kahan_comp" in state:
             return
+        if not param.is_contiguous() and not torch._prims_common.is_non_overlapping_and_dense(param):
+            raise RuntimeError("optimi_b200 needs dense parameters (contiguous or any permutation of contiguous)")
         self._new_state(group, state, param)
         state["kahan_comp"] = self._kahan_state(group, param)
         if group["gradient_release"] and self._counts_steps:
@@ -162,7 +164,7 @@ class OptimiOptimizer(Optimizer):
                     continue
                 type(self)._functional(
                     params, grads, **{self._state_arg_names[k]: v for k, v in lists.items()}, **kw,
-                    kahan_sum=group["kahan_sum"], gradient_release=False, optimizer_accumulation=False,
+                    kahan_sum=group["kahan_sum"], gradient_release=False, optimizer_accumulation=False, _trusted=True,
                 )  # fmt: skip
         else:
             state = self.state[param]
@@ -175,7 +177,7 @@ class OptimiOptimizer(Optimizer):
             type(self)._functional(
                 param, param.grad, **{self._state_arg_names[k]: state[k] for k in self._list_args}, **kw,
                 kahan_sum=group["kahan_sum"], gradient_release=True, optimizer_accumulation=self._optimizer_accumulation,
-                _stream=stream,
+                _stream=stream, _trusted=True,
             )  # fmt: skip
             if stream is not None:
                 param.grad.record_stream(stream)

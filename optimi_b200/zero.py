@@ -1,0 +1,202 @@
+"""ZeRO-1 style sharding of the optimizer step across the GPUs of one node.
+
+The reference has no distributed code; this is the multi-GPU form of the step the build adds.
+Parameters of one dtype are re-pointed into one flat buffer per rank (every rank holds all
+parameters, as in data parallelism).  The flat buffer is cut into `world_size` equal element
+ranges; a rank keeps optimizer states only for its own range, steps only that range — the step is
+element-wise, so a range may start and end in the middle of a tensor — and then one in-place
+all-gather over NCCL hands every rank the updated parameters.  Gradients are expected to be already
+reduced across ranks (that is the job of the data-parallel layer above the optimizer).
+
+StableAdamW is the one optimizer with a per-tensor quantity (the RMS of g^2/v), so its ranges are
+cut on tensor boundaries instead and the exchange is one broadcast per owner of its (unequal) piece.
+
+Sharded and unsharded runs produce bit-identical parameters: each element sees exactly the same
+arithmetic, only on another GPU.
+"""
+
+from __future__ import annotations
+
+from typing import Any, Callable
+
+import torch
+import torch.distributed as dist
+from torch import Tensor
+
+ALIGN_ELEMS = 256  # shard and tensor starts are multiples of this many elements (>= 16 bytes for every dtype)
+
+
+def _round_up(x: int, m: int) -> int:
+    return (x + m - 1) // m * m
+
+
+class FlatLayout:
+    """Where each tensor of one dtype group sits in the flat buffer, and which slice each rank owns."""
+
+    def __init__(self, numels: list[int], world_size: int, split_on_tensors: bool = False):
+        self.numels = list(numels)
+        self.offsets = []
+        off = 0
+        for n in numels:
+            self.offsets.append(off)
+            off = _round_up(off + n, ALIGN_ELEMS)
+        self.total = _round_up(off, ALIGN_ELEMS * world_size)
+        self.world_size = world_size
+        if not split_on_tensors:
+            per = self.total // world_size
+            self.bounds = [r * per for r in range(world_size + 1)]
+        else:
+            # boundaries on tensor starts, each as close as possible to the equal split
+            starts = self.offsets + [self.total]
+            self.bounds = [0]
+            for r in range(1, world_size):
+                target = r * self.total / world_size
+                best = min(starts, key=lambda s: abs(s - target))
+                self.bounds.append(max(best, self.bounds[-1]))
+            self.bounds.append(self.total)
+
+    def rank_range(self, rank: int) -> tuple[int, int]:
+        return self.bounds[rank], self.bounds[rank + 1]
+
+    def pieces(self, rank: int) -> list[tuple[int, int, int]]:
+        """(tensor index, start element within the tensor, end element) of every tensor part in `rank`'s range."""
+        lo, hi = self.rank_range(rank)
+        out = []
+        for i, (off, n) in enumerate(zip(self.offsets, self.numels)):
+            a, b = max(lo, off), min(hi, off + n)
+            if a < b:
+                out.append((i, a - off, b - off))
+        return out
+
+
+class ShardedOptimizer:
+    """Wraps one optimi_b200 (or any torch) optimizer class so that each rank steps 1/world of the elements.
+
+    Args:
+        optimizer_cls: the optimizer class, e.g. ``optimi_b200.AdamW``.
+        params: parameters (one group).  Their storage is moved into flat buffers, values preserved.
+        process_group: the ranks to shard over (default: the world group).
+        split_on_tensors: cut ranges on tensor boundaries (set automatically for StableAdamW).
+        gather: ``"nccl"`` (all-gather after the step) or a callable ``gather(flat, lo, hi)``.
+        **kwargs: passed to the optimizer constructor.
+    """
+
+    def __init__(self, optimizer_cls: Callable, params, process_group=None, split_on_tensors: bool | None = None,
+                 gather: str | Callable = "nccl", **kwargs: Any):  # fmt: skip
+        self.group = process_group
+        self.rank = dist.get_rank(process_group) if dist.is_initialized() else 0
+        self.world = dist.get_world_size(process_group) if dist.is_initialized() else 1
+        self.params = [p for p in params]
+        if split_on_tensors is None:
+            split_on_tensors = getattr(optimizer_cls, "__name__", "") == "StableAdamW"
+        self.gather = gather
+
+        # one flat buffer per (device, dtype)
+        self.buckets: list[dict[str, Any]] = []
+        groups: dict[tuple, list[Tensor]] = {}
+        for p in self.params:
+            groups.setdefault((p.device, p.dtype), []).append(p)
+        shard_params: list[Tensor] = []
+        for (device, dtype), plist in groups.items():
+            layout = FlatLayout([p.numel() for p in plist], self.world, split_on_tensors)
+            flat = torch.zeros(layout.total, dtype=dtype, device=device)
+            for p, off in zip(plist, layout.offsets):
+                view = flat[off : off + p.numel()].view(p.shape)
+                view.copy_(p.data)
+                p.data = view
+            pieces = layout.pieces(self.rank)
+            shards = []
+            for i, a, b in pieces:
+                sp = torch.nn.Parameter(plist[i].data.view(-1)[a:b], requires_grad=True)
+                shards.append(sp)
+            shard_params.extend(shards)
+            self.buckets.append(dict(layout=layout, flat=flat, params=plist, pieces=pieces, shards=shards))
+        self.shard_params = shard_params
+        self.inner = optimizer_cls(shard_params, **kwargs)
+
+    # convenience passthroughs ------------------------------------------------------------------
+    @property
+    def param_groups(self):
+        return self.inner.param_groups
+
+    @property
+    def state(self):
+        return self.inner.state
+
+    def local_elements(self) -> int:
+        return sum(sp.numel() for sp in self.shard_params)
+
+    def _bind_grads(self):
+        for b in self.buckets:
+            for (i, a, e), sp in zip(b["pieces"], b["shards"]):
+                g = b["params"][i].grad
+                if g is None:
+                    sp.grad = None
+                    continue
+                if not g.is_contiguous():
+                    raise RuntimeError("ShardedOptimizer needs contiguous gradients")
+                sp.grad = g.view(-1)[a:e]
+
+    @torch.no_grad()
+    def step_local(self, shard_grads: list[Tensor] | None = None):
+        """Steps this rank's range only (no exchange).  `shard_grads`, one tensor per entry of
+        `shard_params`, bypasses the parameters' `.grad` (a rank that received only its slice of the
+        gradients from a reduce-scatter has nothing else)."""
+        if shard_grads is None:
+            self._bind_grads()
+        else:
+            for sp, g in zip(self.shard_params, shard_grads):
+                sp.grad = g
+        self.inner.step()
+
+    @torch.no_grad()
+    def gather_params(self):
+        """Hands every rank the updated parameters: one in-place all-gather per flat buffer."""
+        if self.world == 1:
+            return
+        for b in self.buckets:
+            layout, flat = b["layout"], b["flat"]
+            lo, hi = layout.rank_range(self.rank)
+            if callable(self.gather):
+                self.gather(flat, lo, hi)
+                continue
+            sizes = [layout.bounds[r + 1] - layout.bounds[r] for r in range(self.world)]
+            if all(s == sizes[0] for s in sizes):
+                dist.all_gather_into_tensor(flat, flat[lo:hi], group=self.group)
+            else:
+                # unequal pieces (ranges cut on tensor boundaries): one broadcast per owner
+                for r in range(self.world):
+                    piece = flat[layout.bounds[r] : layout.bounds[r + 1]]
+                    if piece.numel():
+                        src = dist.get_global_rank(self.group, r) if self.group is not None else r
+                        dist.broadcast(piece, src=src, group=self.group)
+
+    @torch.no_grad()
+    def step(self, shard_grads: list[Tensor] | None = None):
+        self.step_local(shard_grads)
+        self.gather_params()
+
+    def zero_grad(self, set_to_none: bool = True):
+        for p in self.params:
+            if p.grad is not None:
+                if set_to_none:
+                    p.grad = None
+                else:
+                    p.grad.zero_()
+        for sp in self.shard_params:
+            sp.grad = None
+
+    # checkpoints -------------------------------------------------------------------------------
+    def state_dict(self) -> dict[str, Any]:
+        """This rank's shard of the optimizer state plus the layout needed to put shards back together."""
+        return {
+            "inner": self.inner.state_dict(),
+            "rank": self.rank,
+            "world": self.world,
+            "pieces": [b["pieces"] for b in self.buckets],
+        }
+
+    def load_state_dict(self, sd: dict[str, Any]) -> None:
+        if sd["world"] != self.world or sd["rank"] != self.rank:
+            raise ValueError(f"shard of rank {sd['rank']}/{sd['world']} loaded into rank {self.rank}/{self.world}")
+        self.inner.load_state_dict(sd["inner"])

@@ -1,0 +1,96 @@
+"""Host logic of the ZeRO-1 wrapper on CPU: layouts, and a 2-rank gloo run whose sharded result must
+equal the unsharded one bit for bit (with a torch optimizer standing in for the CUDA kernels)."""
+
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from optimi_b200.zero import ALIGN_ELEMS, FlatLayout, ShardedOptimizer
+
+
+def test_flat_layout_equal_split_covers_everything_once():
+    numels = [1000, 7, 4096, 123457, 1]
+    for world in (1, 2, 3, 8):
+        lay = FlatLayout(numels, world)
+        assert lay.total % (ALIGN_ELEMS * world) == 0
+        assert all(o % ALIGN_ELEMS == 0 for o in lay.offsets)
+        seen = [0] * len(numels)
+        sizes = set()
+        for r in range(world):
+            lo, hi = lay.rank_range(r)
+            sizes.add(hi - lo)
+            for i, a, b in lay.pieces(r):
+                assert 0 <= a < b <= numels[i]
+                assert (lay.offsets[i] + a) % 8 == 0 or a == 0
+                seen[i] += b - a
+        assert seen == numels and len(sizes) == 1
+
+
+def test_flat_layout_tensor_split_never_cuts_a_tensor():
+    numels = [500_000, 4096, 300_000, 300_000, 4096, 900_000, 16]
+    for world in (2, 4):
+        lay = FlatLayout(numels, world, split_on_tensors=True)
+        owners = {}
+        for r in range(world):
+            for i, a, b in lay.pieces(r):
+                assert (a, b) == (0, numels[i])
+                owners[i] = r
+        assert sorted(owners) == list(range(len(numels)))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, split_on_tensors, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        g = torch.Generator().manual_seed(0)
+        shapes = [(33, 65), (129,), (1024, 3), (7,), (2000,)]
+        params = [torch.nn.Parameter(torch.randn(s, generator=g)) for s in shapes]
+        ref = [torch.nn.Parameter(p.detach().clone()) for p in params]
+        sharded = ShardedOptimizer(torch.optim.AdamW, params, split_on_tensors=split_on_tensors, lr=1e-2, weight_decay=0.1)
+        plain = torch.optim.AdamW(ref, lr=1e-2, weight_decay=0.1)
+        for step in range(4):
+            grads = [torch.randn(s, generator=g) for s in shapes]
+            for p, r, gr in zip(params, ref, grads):
+                p.grad, r.grad = gr.clone(), gr.clone()
+            sharded.step()
+            plain.step()
+            sharded.zero_grad()
+        ok = all(torch.equal(p.detach(), r.detach()) for p, r in zip(params, ref))
+        n_local = sharded.local_elements()
+        gathered = [None] * world
+        dist.all_gather_object(gathered, n_local)
+        sd = sharded.state_dict()
+        assert sd["rank"] == rank and sd["world"] == world
+        sharded.load_state_dict(sd)
+        if rank == 0:
+            out.put((ok, gathered, sum(p.numel() for p in params)))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("split_on_tensors", [False, True])
+def test_two_ranks_match_unsharded(split_on_tensors):
+    ctx = mp.get_context("spawn")
+    out = ctx.SimpleQueue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, split_on_tensors, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    ok, local_sizes, total = out.get()
+    assert ok, "sharded parameters differ from the unsharded run"
+    assert sum(local_sizes) == total
+    if not split_on_tensors:
+        assert abs(local_sizes[0] - local_sizes[1]) <= 2 * ALIGN_ELEMS * 6
