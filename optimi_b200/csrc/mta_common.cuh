@@ -5,10 +5,10 @@
 // needs no device-side metadata buffer, no host-to-device copy and no allocation.
 //
 // Work decomposition, chosen by measurement on a B200: tensors are cut into small fixed tiles of
-// kThreads * U vectors (16 bytes each); one 256-thread block owns one tile, issues ALL of its loads
+// kThreads * U vectors (16 bytes each); one 128-thread block owns one tile, issues ALL of its loads
 // up front (U vectors per stream per thread), computes, stores and exits.  Millions of short-lived
 // blocks keep every SM's memory pipeline full without a persistent loop, and a register budget
-// around 50 leaves five blocks resident per SM.  Block b finds its tensor through a 256-entry
+// around 50 leaves ten blocks resident per SM.  Block b finds its tensor through a 256-entry
 // coarse index over the block range plus a short forward walk over the prefix sum of block counts
 // (a plain binary search over the table cost 10-20 % of the step: every probe is a dependent,
 // dynamically indexed read of kernel-parameter space).
@@ -22,7 +22,7 @@
 namespace optimi {
 
 #ifndef OPTIMI_THREADS
-#define OPTIMI_THREADS 256
+#define OPTIMI_THREADS 128
 #endif
 constexpr int kThreads = OPTIMI_THREADS;  // threads per block
 constexpr int kTableBytes = 29440;  // budget for the per-tensor arrays of one by-value table
@@ -196,6 +196,7 @@ __device__ __forceinline__ bool tile_pointers(const MtaTable<NL>& tab, const Spa
 //   writes(l, args)           list l is stored back   (uniform across the launch)
 //   elem<T>(e, args, ctx)     the arithmetic for ONE element; e[l] is the element of list l as fp32
 //   kSumSlot                  index of an e[] slot whose values compute_vec sums up (-1: none)
+//   kMinBlocks                blocks that must fit on one SM (register cap for the compiler)
 // ---------------------------------------------------------------------------------------------
 struct NoCtx {};
 
@@ -298,8 +299,16 @@ __device__ __forceinline__ double process_tile(const MtaTable<Op::NL>& tab, cons
   return acc;
 }
 
+// Op::kMinBlocks caps the registers per thread (65536 / (kThreads * kMinBlocks)): residency, not
+// per-thread instruction-level parallelism, is what keeps the memory pipeline full here.
+// fp16 needs the IEEE square root and a two-instruction rounding, hence a slightly larger budget.
 template <typename T, class Op>
-__global__ void __launch_bounds__(kThreads) mta_kernel(const __grid_constant__ MtaTable<Op::NL> tab,
+constexpr int min_blocks() {
+  return sizeof(T) == 2 && !__is_same(T, __nv_bfloat16) ? (Op::kMinBlocks > 2 ? Op::kMinBlocks - 2 : 1) : Op::kMinBlocks;
+}
+
+template <typename T, class Op>
+__global__ void __launch_bounds__(kThreads, min_blocks<T, Op>()) mta_kernel(const __grid_constant__ MtaTable<Op::NL> tab,
                                                        const __grid_constant__ typename Op::Args args) {
   Span s;
   process_tile<T, Op>(tab, args, s);

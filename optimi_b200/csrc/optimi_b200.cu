@@ -150,7 +150,7 @@ static int dispatch(const char* name, int dtype, bool kahan, bool update, int n,
 // g^2 / max(v, eps^2) to partial[tile] — one double per tile, written (not accumulated), so the
 // scratch needs no clearing and the result does not depend on block scheduling.
 template <typename T>
-__global__ void __launch_bounds__(kThreads) stable_moments_sum_kernel(const __grid_constant__ MtaTable<4> tab,
+__global__ void __launch_bounds__(kThreads, 10) stable_moments_sum_kernel(const __grid_constant__ MtaTable<4> tab,
                                                                       const __grid_constant__ StableMomentsArgs a,
                                                                       double* __restrict__ partial) {
   Span s;
@@ -266,7 +266,9 @@ static int stableadamw_typed(int n, void* const* params, void* const* grads, voi
   ua.eps = (float)eps;
   ua.has_wd = weight_decay != 0;
   void* const* const lists_b[4] = {params, exp_avgs, exp_avg_sqs, kahan ? kahan_comps : nullptr};
-  if (kahan) return launch_op<T, StableUpdateOp<true>>("optimi_b200_stableadamw (update)", n, numels, lists_b, ua, stream);
+  if constexpr (sizeof(T) == 2) {  // Kahan compensation exists for the 16-bit storage types only
+    if (kahan) return launch_op<T, StableUpdateOp<true>>("optimi_b200_stableadamw (update)", n, numels, lists_b, ua, stream);
+  }
   return launch_op<T, StableUpdateOp<false>>("optimi_b200_stableadamw (update)", n, numels, lists_b, ua, stream);
 }
 

@@ -65,6 +65,7 @@ __device__ __forceinline__ void weight_decay(float& p, float& g, int mode, float
 struct OpBase {
   using Ctx = NoCtx;
   static constexpr int kSumSlot = -1;
+  static constexpr int kMinBlocks = 10;  // <= 51 registers per thread at 128 threads
   template <class Table, class Args>
   static __device__ __forceinline__ NoCtx context(const Table&, const Span&, const Args&) { return NoCtx{}; }
 };
@@ -116,6 +117,7 @@ struct RangerArgs {
 template <bool KAHAN, bool UPDATE>
 struct RangerOp : OpBase {
   static constexpr int NL = 6, U = OPTIMI_U_ADAM;
+  static constexpr int kMinBlocks = 8;  // six streams: <= 64 registers
   using Args = RangerArgs;
   static __device__ __forceinline__ bool reads(int l, const Args& a) {
     return l == 0 ? UPDATE : l == 4 ? KAHAN : l == 5 ? (UPDATE && a.lookahead) : true;
@@ -245,6 +247,7 @@ struct AdanArgs {
 template <bool KAHAN, bool UPDATE>
 struct AdanOp : OpBase {
   static constexpr int NL = 7, U = OPTIMI_U_WIDE;
+  static constexpr int kMinBlocks = 7;  // seven streams: <= 73 registers
   using Args = AdanArgs;
   static __device__ __forceinline__ bool reads(int l, const Args&) { return l == 0 ? UPDATE : l == 6 ? KAHAN : true; }
   static __device__ __forceinline__ bool writes(int l, const Args& a) { return l != 1 && reads(l, a); }
@@ -317,6 +320,7 @@ template <bool KAHAN>
 struct StableUpdateOp {
   static constexpr int NL = 4, U = OPTIMI_U_NARROW;
   static constexpr int kSumSlot = -1;
+  static constexpr int kMinBlocks = 10;
   using Args = StableUpdateArgs;
   using Ctx = float2;
   template <class Table>
