@@ -95,6 +95,39 @@ int optimi_b200_stableadamw(int n_tensors, void* const* params, void* const* gra
                             double eps, int decouple_lr, double max_lr, int kahan_sum, int update_parameters,
                             void* workspace, size_t workspace_bytes, void* stream);
 
+/* StableAdamW for callers that have no device memory to hand over.  No counterpart in the reference:
+ * its StableAdamW keeps its scratch in ordinary PyTorch tensors and never faces the question.
+ *
+ * Who this is for: code that gets the parameter, gradient and state pointers from somebody else and
+ * has no allocator of its own to call — a plugin inside a runtime that owns all device memory and
+ * forbids cudaMalloc after start-up, a step running where an allocation is not allowed to happen
+ * (cudaMalloc synchronises the whole device and can fail under memory pressure, which a training
+ * loop that has planned its memory to the last gigabyte cannot tolerate), or a binding in a
+ * language whose CUDA wrapper exposes launches but not allocation.  Such a caller cannot satisfy
+ * the `workspace` argument of optimi_b200_stableadamw.  Here the scratch is a fixed array of
+ * OPTIMI_B200_STATIC_SCRATCH_BYTES inside the library image; every GPU that loads the library
+ * carries it until the process exits.
+ *
+ * Same arguments and results as optimi_b200_stableadamw without `workspace`/`workspace_bytes`
+ * (results are bit-identical for the same inputs).  Limits and rules:
+ *   - The list must need no more scratch than the array holds: 8 bytes per tensor plus 8 bytes per
+ *     tile of 1024 (bf16/fp16) or 512 (fp32) elements, i.e. about 536 M bf16 or 268 M fp32 elements
+ *     per call.  Larger lists are rejected with OPTIMI_ERR_WORKSPACE_TOO_SMALL before anything is
+ *     launched; split them into several calls (the optimizer is per-tensor, so that is exact).
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
+ *     that device current).  Make that first call outside any stream capture.
+ *   - All calls on a device share the one array and it keeps the previous call's contents.  Nothing
+ *     in it has to start at zero (every slot is written before it is read within a call), but two
+ *     calls that overlap on the GPU — different streams without an ordering between them — race
+ *     on it.  Calls on one stream, or ordered by events, are fine.
+ *   - Calls cudaMalloc, cudaFree or any allocating routine: never. */
+#define OPTIMI_B200_STATIC_SCRATCH_BYTES (4u << 20)
+int optimi_b200_stableadamw_static(int n_tensors, void* const* params, void* const* grads, void* const* exp_avgs,
+                                   void* const* exp_avg_sqs, void* const* kahan_comps, const int64_t* numels, int dtype,
+                                   double lr, double beta1_comp, double beta2_hat, double beta2_comp, double weight_decay,
+                                   double eps, int decouple_lr, double max_lr, int kahan_sum, int update_parameters,
+                                   void* stream);
+
 /* Adan.  Replaces _foreach_adan (optimi/adan.py:472-546), _single_param_adan (optimi/adan.py:405-469)
  * and the Triton launchers (optimi/adan.py:652-770).  `prev_grads` holds the NEGATED previous
  * gradient (optimi/adan.py:109).  `weight_decay` is the folded factor 1 + lr*wd (Adan style,

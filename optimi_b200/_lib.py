@@ -30,6 +30,7 @@ SIGNATURES = {
     "optimi_b200_lion": [_I] + [_P] * 4 + [_P, _I] + [_D] * 4 + [_I] * 2 + [_P],
     "optimi_b200_sgd": [_I] + [_P] * 4 + [_P, _I] + [_D] * 3 + [_I] * 4 + [_P],
     "optimi_b200_stableadamw": [_I] + [_P] * 5 + [_P, _I] + [_D] * 6 + [_I, _D, _I, _I, _P, ctypes.c_size_t, _P],
+    "optimi_b200_stableadamw_static": [_I] + [_P] * 5 + [_P, _I] + [_D] * 6 + [_I, _D, _I, _I, _P],
     "optimi_b200_adan": [_I] + [_P] * 7 + [_P, _I] + [_D] * 8 + [_I] * 3 + [_P],
     "optimi_b200_radam": [_I] + [_P] * 5 + [_P, _I] + [_D] * 6 + [_I, _D] + [_I] * 3 + [_P],
     "optimi_b200_ranger": [_I] + [_P] * 6 + [_P, _I] + [_D] * 6 + [_I, _D, _I, _D] + [_I] * 3 + [_P],

@@ -8,6 +8,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 #include <type_traits>
 
 #include "optimizer_ops.cuh"
@@ -460,3 +461,87 @@ int optimi_b200_stableadamw(int n, void* const* params, void* const* grads, void
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// StableAdamW without any caller-provided scratch
+// ---------------------------------------------------------------------------------------------
+namespace optimi {
+
+// Scratch that lives in the library image itself.  The name below is only a host-side handle: the
+// device address is looked up once per device with cudaGetSymbolAddress and that pointer is what
+// the kernels receive.
+static __device__ __align__(256) unsigned char g_static_scratch[OPTIMI_B200_STATIC_SCRATCH_BYTES];
+
+constexpr int kMaxDevices = 64;
+static std::mutex g_static_scratch_mutex;
+static void* g_static_scratch_ptr[kMaxDevices] = {};
+
+static int static_scratch_of_current_device(void** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(OPTIMI_ERR_CUDA, "optimi_b200_stableadamw_static: cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices)
+    return fail(OPTIMI_ERR_INVALID_ARGUMENT, "optimi_b200_stableadamw_static: device index %d is outside 0..%d", dev, kMaxDevices - 1);
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (!g_static_scratch_ptr[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (e != cudaSuccess || !p)
+      return fail(OPTIMI_ERR_CUDA, "optimi_b200_stableadamw_static: cudaGetSymbolAddress on device %d: %s", dev, cudaGetErrorString(e));
+    g_static_scratch_ptr[dev] = p;
+  }
+  *out = g_static_scratch_ptr[dev];
+  return OPTIMI_OK;
+}
+
+template <typename T>
+static size_t stable_scratch_need(int n, const int64_t* numels) {
+  return align_up((size_t)n * sizeof(float2), 16) + (size_t)count_tiles(n, numels, tile_of<T, StableMomentsOp<true>>()) * sizeof(double);
+}
+
+}  // namespace optimi
+
+extern "C" int optimi_b200_stableadamw_static(int n, void* const* params, void* const* grads, void* const* exp_avgs,
+                                              void* const* exp_avg_sqs, void* const* kahan_comps, const int64_t* numels,
+                                              int dtype, double lr, double beta1_comp, double beta2_hat, double beta2_comp,
+                                              double weight_decay, double eps, int decouple_lr, double max_lr, int kahan_sum,
+                                              int update_parameters, void* stream) {
+  const char* fn = "optimi_b200_stableadamw_static";
+  const bool update = update_parameters != 0;
+  const bool kahan = update && kahan_sum && kahan_comps && low_precision(dtype);
+  void* const* const lists[5] = {params, grads, exp_avgs, exp_avg_sqs, kahan ? kahan_comps : nullptr};
+  const bool req[5] = {update, true, true, true, kahan};
+  static const char* const names[5] = {"params", "grads", "exp_avgs", "exp_avg_sqs", "kahan_comps"};
+  int rc = check_lists(fn, n, numels, dtype, 5, lists, req, names);
+  if (rc != OPTIMI_OK || n == 0) return rc;
+  if (update && weight_decay != 0 && decouple_lr && !(max_lr > 0))
+    return fail(OPTIMI_ERR_INVALID_ARGUMENT, "%s: decouple_lr needs max_lr > 0", fn);
+
+  void* scratch = nullptr;
+  if (update) {  // the accumulate-only micro-step needs no scratch at all
+    const size_t need = dtype == OPTIMI_F32    ? stable_scratch_need<float>(n, numels)
+                        : dtype == OPTIMI_BF16 ? stable_scratch_need<__nv_bfloat16>(n, numels)
+                                               : stable_scratch_need<__half>(n, numels);
+    if (need > (size_t)OPTIMI_B200_STATIC_SCRATCH_BYTES)
+      return fail(OPTIMI_ERR_WORKSPACE_TOO_SMALL,
+                  "%s: this tensor list needs %zu bytes of scratch, the built-in scratch holds %zu; split the list into "
+                  "several calls or use optimi_b200_stableadamw with your own workspace",
+                  fn, need, (size_t)OPTIMI_B200_STATIC_SCRATCH_BYTES);
+    rc = static_scratch_of_current_device(&scratch);
+    if (rc != OPTIMI_OK) return rc;
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+  const size_t cap = (size_t)OPTIMI_B200_STATIC_SCRATCH_BYTES;
+  switch (dtype) {
+    case OPTIMI_F32:
+      return stableadamw_typed<float>(n, params, grads, exp_avgs, exp_avg_sqs, kahan_comps, numels, lr, beta1_comp, beta2_hat,
+                                      beta2_comp, weight_decay, eps, decouple_lr, max_lr, false, update, scratch, cap, s);
+    case OPTIMI_BF16:
+      return stableadamw_typed<__nv_bfloat16>(n, params, grads, exp_avgs, exp_avg_sqs, kahan_comps, numels, lr, beta1_comp,
+                                              beta2_hat, beta2_comp, weight_decay, eps, decouple_lr, max_lr, kahan, update,
+                                              scratch, cap, s);
+    default:
+      return stableadamw_typed<__half>(n, params, grads, exp_avgs, exp_avg_sqs, kahan_comps, numels, lr, beta1_comp, beta2_hat,
+                                       beta2_comp, weight_decay, eps, decouple_lr, max_lr, kahan, update, scratch, cap, s);
+  }
+}
