@@ -65,14 +65,15 @@ def numel(shape):
     return math.prod(shape)
 
 
-def make_config(workload: str, n_gpus: int) -> dict:
+def make_config(workload: str, n_gpus: int, exchange: str = "auto") -> dict:
     """The `config` object of the JSON line; identical for both arms of one (workload, N)."""
     shapes = WORKLOADS[workload]()
     n_params = sum(numel(s) for s in shapes)
     return {
         "workload": f"AdamW bf16+Kahan, decouple_lr, {workload} parameter shapes ({n_params} params, {len(shapes)} tensors)",
         "optimizer": "AdamW", "lr": HYPER["lr"], "weight_decay": HYPER["weight_decay"], "decouple_lr": True,
-        "sharding": "none" if n_gpus == 1 else f"ZeRO-1 over {n_gpus} ranks, NCCL all-gather of updated params",
+        "sharding": "none" if n_gpus == 1 else f"ZeRO-1 over {n_gpus} ranks, exchange={exchange} "
+                    "(push: step kernel stores updated params into the peers over NVLink; nccl: all-gather after the step)",
         "l2": "inputs larger than L2, no flush between steps: %.1f GB streamed per rank per step" % (BYTES_PER_PARAM * n_params / n_gpus / 1e9),
     }  # fmt: skip
 
@@ -257,7 +258,7 @@ def run_reference_arm(args):
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": done,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
-        "config": make_config(args.workload, args.gpus),
+        "config": make_config(args.workload, args.gpus, args.exchange),
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -288,7 +289,7 @@ def run_b200_arm(args):
         step_targets = params
         sharded = None
     else:
-        sharded = ShardedOptimizer(optimi_b200.AdamW, params, **HYPER)
+        sharded = ShardedOptimizer(optimi_b200.AdamW, params, exchange=args.exchange, **HYPER)
         opt = sharded
         step_targets = sharded.shard_params
     n_local = sum(t.numel() for t in step_targets)
@@ -410,7 +411,8 @@ def run_b200_arm(args):
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
-        "config": make_config(args.workload, world),
+        "config": make_config(args.workload, world, args.exchange),
+        "exchange": None if sharded is None else sharded.exchange,
         "hbm_gbs": achieved, "step_ms": step_ms_max, "gather_ms": gather_ms_max, "wall_ms_per_step": t_wall * 1e3 / args.steps,
         "roofline": roofline, "cpu_baseline": cpu,
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
@@ -428,6 +430,7 @@ def main():
     ap.add_argument("--impl", default="optimi_b200", choices=["optimi_b200", "reference"])
     ap.add_argument("--workload", default="llama3-8b", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--exchange", default="auto", choices=["auto", "push", "nccl"], help="N>1: how updated parameters reach the other ranks")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)

@@ -27,6 +27,7 @@ _I = ctypes.c_int
 # name -> argument types after (n_tensors) and the pointer lists; mirrors include/optimi_b200.h
 SIGNATURES = {
     "optimi_b200_adam": [_I] + [_P] * 5 + [_P, _I] + [_D] * 6 + [_I] * 3 + [_P],
+    "optimi_b200_adam_push": [_I] + [_P] * 5 + [_P, _I] + [_D] * 6 + [_I] * 2 + [_I, _P, _P],
     "optimi_b200_lion": [_I] + [_P] * 4 + [_P, _I] + [_D] * 4 + [_I] * 2 + [_P],
     "optimi_b200_sgd": [_I] + [_P] * 4 + [_P, _I] + [_D] * 3 + [_I] * 4 + [_P],
     "optimi_b200_stableadamw": [_I] + [_P] * 5 + [_P, _I] + [_D] * 6 + [_I, _D, _I, _I, _P, ctypes.c_size_t, _P],

@@ -188,6 +188,30 @@ __device__ __forceinline__ bool tile_pointers(const MtaTable<NL>& tab, const Spa
 }
 
 // ---------------------------------------------------------------------------------------------
+// Peer push: the fused form of "step, then all-gather the updated parameters".  Every rank holds
+// the parameter buffer at its own virtual address; `delta[j]` is the byte distance from this rank's
+// copy to peer j's copy as mapped into this process (symmetric memory over NVLink).  A block that
+// has just produced an updated parameter vector stores it locally and, with plain st.global, at the
+// same offset in each peer's copy, so the exchange rides along with the step tile by tile.  Plain
+// peer stores only, no waits on other ranks inside the kernel (the ranks meet in a
+// tiny stream-ordered collective after the launch).
+// ---------------------------------------------------------------------------------------------
+constexpr int kMaxPeers = 7;
+struct PeerPush {
+  int n;
+  long long delta[kMaxPeers];
+};
+template <typename T>
+__device__ __forceinline__ void push_vec(const PeerPush& push, T* local, uint4 v) {
+  for (int j = 0; j < push.n; j++)
+    *reinterpret_cast<uint4*>(reinterpret_cast<char*>(local) + push.delta[j]) = v;
+}
+template <typename T>
+__device__ __forceinline__ void push_one(const PeerPush& push, T* local, T v) {
+  for (int j = 0; j < push.n; j++) *reinterpret_cast<T*>(reinterpret_cast<char*>(local) + push.delta[j]) = v;
+}
+
+// ---------------------------------------------------------------------------------------------
 // Generic element-wise machinery.  An Op describes one optimizer variant:
 //   NL, U                     number of tensor lists, vectors per thread per list in a full tile
 //   Args                      uniform scalars of the launch
@@ -197,6 +221,7 @@ __device__ __forceinline__ bool tile_pointers(const MtaTable<NL>& tab, const Spa
 //   elem<T>(e, args, ctx)     the arithmetic for ONE element; e[l] is the element of list l as fp32
 //   kSumSlot                  index of an e[] slot whose values compute_vec sums up (-1: none)
 //   kMinBlocks                blocks that must fit on one SM (register cap for the compiler)
+//   kPush                     also store updated parameters into the peers' copies (Args has .push)
 // ---------------------------------------------------------------------------------------------
 struct NoCtx {};
 
@@ -214,6 +239,9 @@ __device__ __forceinline__ void store_vec(const Vecs<Op::NL>& v, T* const (&p)[O
 #pragma unroll
   for (int l = 0; l < Op::NL; l++)
     if (Op::writes(l, a)) stv(p[l] + i, v.r[l]);
+  if constexpr (Op::kPush) {  // list 0 is the parameter list in every op that can push
+    if (Op::writes(0, a)) push_vec(a.push, p[0] + i, v.r[0]);
+  }
 }
 
 template <typename T, class Op>
@@ -256,6 +284,9 @@ __device__ __forceinline__ float scalar_elem(T* const (&p)[Op::NL], int i, const
 #pragma unroll
   for (int l = 0; l < Op::NL; l++)
     if (Op::writes(l, a)) Pack<T>::store1(p[l] + i, e[l]);
+  if constexpr (Op::kPush) {
+    if (Op::writes(0, a)) push_one(a.push, p[0] + i, p[0][i]);
+  }
   return Op::kSumSlot >= 0 ? e[Op::kSumSlot < 0 ? 0 : Op::kSumSlot] : 0.f;
 }
 

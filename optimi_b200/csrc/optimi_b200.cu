@@ -314,6 +314,34 @@ int optimi_b200_adam(int n, void* const* params, void* const* grads, void* const
   return dispatch<AdamOp>("optimi_b200_adam", dtype, kahan, update, n, numels, lists, a, (cudaStream_t)stream);
 }
 
+int optimi_b200_adam_push(int n, void* const* params, void* const* grads, void* const* exp_avgs, void* const* exp_avg_sqs,
+                          void* const* kahan_comps, const int64_t* numels, int dtype, double lr, double beta1_comp,
+                          double beta2_hat, double beta2_comp, double weight_decay, double eps, int decouple_wd, int kahan_sum,
+                          int n_peers, const int64_t* peer_deltas, void* stream) {
+  const char* fn = "optimi_b200_adam_push";
+  if (n_peers < 0 || n_peers > kMaxPeers) return fail(OPTIMI_ERR_INVALID_ARGUMENT, "%s: n_peers=%d is outside 0..%d", fn, n_peers, kMaxPeers);
+  if (n_peers > 0 && !peer_deltas) return fail(OPTIMI_ERR_INVALID_ARGUMENT, "%s: peer_deltas is NULL", fn);
+  const bool kahan = kahan_sum && kahan_comps && low_precision(dtype);
+  void* const* const lists[5] = {params, grads, exp_avgs, exp_avg_sqs, kahan ? kahan_comps : nullptr};
+  const bool req[5] = {true, true, true, true, kahan};
+  static const char* const names[5] = {"params", "grads", "exp_avgs", "exp_avg_sqs", "kahan_comps"};
+  int rc = check_lists(fn, n, numels, dtype, 5, lists, req, names);
+  if (rc != OPTIMI_OK || n == 0) return rc;
+  PushArgs<AdamArgs> a;
+  a.base.l1 = make_lerp(beta1_comp);
+  a.base.beta2_hat = (float)beta2_hat;
+  a.base.beta2_comp = (float)beta2_comp;
+  a.base.wd = (float)weight_decay;
+  a.base.eps = (float)eps;
+  a.base.neg_lr = (float)(-lr);
+  a.base.wd_mode = wd_mode_of(weight_decay, decouple_wd);
+  a.push.n = n_peers;
+  for (int j = 0; j < kMaxPeers; j++) a.push.delta[j] = j < n_peers ? (long long)peer_deltas[j] : 0;
+  for (int j = 0; j < n_peers; j++)
+    if (peer_deltas[j] % 16) return fail(OPTIMI_ERR_INVALID_ARGUMENT, "%s: peer_deltas[%d] is not a multiple of 16 bytes", fn, j);
+  return dispatch<AdamPushOp>(fn, dtype, kahan, true, n, numels, lists, a, (cudaStream_t)stream);
+}
+
 int optimi_b200_radam(int n, void* const* params, void* const* grads, void* const* exp_avgs, void* const* exp_avg_sqs,
                       void* const* kahan_comps, const int64_t* numels, int dtype, double lr, double beta1_comp,
                       double beta2_hat, double beta2_comp, double weight_decay, double eps, int use_rect, double rect,

@@ -66,6 +66,7 @@ struct OpBase {
   using Ctx = NoCtx;
   static constexpr int kSumSlot = -1;
   static constexpr int kMinBlocks = 10;  // <= 51 registers per thread at 128 threads
+  static constexpr bool kPush = false;
   template <class Table, class Args>
   static __device__ __forceinline__ NoCtx context(const Table&, const Span&, const Args&) { return NoCtx{}; }
 };
@@ -102,6 +103,31 @@ struct AdamOp : OpBase {
     }
   }
 };
+
+// Any op whose list 0 is the parameter list, with the peer push added to its stores.
+template <class BaseArgs>
+struct PushArgs {
+  BaseArgs base;
+  PeerPush push;
+};
+
+template <class Base>
+struct PushOp {
+  static constexpr int NL = Base::NL, U = Base::U, kSumSlot = Base::kSumSlot;
+  static constexpr int kMinBlocks = Base::kMinBlocks > 2 ? Base::kMinBlocks - 2 : 1;
+  static constexpr bool kPush = true;
+  using Args = PushArgs<typename Base::Args>;
+  using Ctx = typename Base::Ctx;
+  template <class Table>
+  static __device__ __forceinline__ Ctx context(const Table& tab, const Span& s, const Args& a) { return Base::context(tab, s, a.base); }
+  static __device__ __forceinline__ bool reads(int l, const Args& a) { return Base::reads(l, a.base); }
+  static __device__ __forceinline__ bool writes(int l, const Args& a) { return Base::writes(l, a.base); }
+  template <typename T>
+  static __device__ __forceinline__ void elem(float (&e)[NL], const Args& a, const Ctx& ctx) { Base::template elem<T>(e, a.base, ctx); }
+};
+
+template <bool KAHAN, bool UPDATE>
+using AdamPushOp = PushOp<AdamOp<KAHAN, UPDATE>>;
 
 // ---------------------------------------------------------------------------------------------
 // RAdam and Ranger              lists: 0 p, 1 g, 2 m, 3 v, 4 k, 5 la (slow weights, Ranger only)
@@ -321,6 +347,7 @@ struct StableUpdateOp {
   static constexpr int NL = 4, U = OPTIMI_U_NARROW;
   static constexpr int kSumSlot = -1;
   static constexpr int kMinBlocks = 10;
+  static constexpr bool kPush = false;
   using Args = StableUpdateArgs;
   using Ctx = float2;
   template <class Table>

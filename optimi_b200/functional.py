@@ -86,13 +86,29 @@ def adam(
     optimizer_accumulation: bool = False,
     _stream=None,
     _trusted: bool = False,
+    _push=None,
 ):
-    """Adam / AdamW step on lists of tensors (or bare tensors in gradient-release form)."""
+    """Adam / AdamW step on lists of tensors (or bare tensors in gradient-release form).
+
+    `_push` (a sequence of byte offsets to the peers' copies of the parameter buffer) selects the
+    fused step + exchange kernel of a sharded run; see `optimi_b200.zero.ShardedOptimizer`.
+    """
     t = _advance(step)
     beta1_comp = 1 - debias_beta(beta1, t)
     beta2_hat = debias_beta(beta2, t)
     beta2_comp = 1 - beta2_hat
     wd = _fold_weight_decay(weight_decay, lr, decouple_wd, decouple_lr, max_lr)
+    if _push is not None and not optimizer_accumulation:
+        import ctypes
+
+        deltas = (ctypes.c_int64 * len(_push))(*_push)
+        tail = (lr, beta1_comp, beta2_hat, beta2_comp, wd, eps, int(decouple_wd or decouple_lr), int(bool(kahan_sum)),
+                len(_push), ctypes.cast(deltas, ctypes.c_void_p))  # fmt: skip
+        launch(
+            "optimi_b200_adam_push", [params, grads, exp_avgs, exp_avg_sqs, kahan_comps],
+            ("params", "grads", "exp_avgs", "exp_avg_sqs", "kahan_comps"), lambda *_: tail, _stream, _trusted,
+        )  # fmt: skip
+        return
     tail = (lr, beta1_comp, beta2_hat, beta2_comp, wd, eps, int(decouple_wd or decouple_lr), int(bool(kahan_sum)),
             int(not optimizer_accumulation))  # fmt: skip
     launch(
@@ -123,12 +139,13 @@ def adamw(
     optimizer_accumulation: bool = False,
     _stream=None,
     _trusted: bool = False,
+    _push=None,
 ):
     """AdamW step: `adam` with decoupled weight decay (optimi/adamw.py:123-143)."""
     adam(
         params, grads, exp_avgs, exp_avg_sqs, kahan_comps, lr=lr, beta1=beta1, beta2=beta2, weight_decay=weight_decay,
         eps=eps, step=step, decouple_wd=True, decouple_lr=decouple_lr, max_lr=max_lr, kahan_sum=kahan_sum,
-        gradient_release=gradient_release, optimizer_accumulation=optimizer_accumulation, _stream=_stream, _trusted=_trusted,
+        gradient_release=gradient_release, optimizer_accumulation=optimizer_accumulation, _stream=_stream, _trusted=_trusted, _push=_push,
     )  # fmt: skip
 
 

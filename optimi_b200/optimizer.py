@@ -36,6 +36,7 @@ class OptimiOptimizer(Optimizer):
     _list_args: tuple[str, ...] = ()  # functional list arguments after params, grads, in order; names of state keys
     _state_arg_names: dict[str, str] = {}  # state key -> functional keyword
     _counts_steps = True  # keeps a `step` counter (Lion and SGD do not)
+    _supports_push = False  # has a fused step + peer-push kernel (sharded runs)
     _scalar_keys: tuple[str, ...] = ()  # param_group keys forwarded as keywords
 
     def __init__(self, params: Iterable[Tensor] | Iterable[dict], defaults: dict[str, Any]):
@@ -71,6 +72,7 @@ class OptimiOptimizer(Optimizer):
                 )
 
         self._optimizer_accumulation = False
+        self._peer_push: list[int] | None = None  # set by zero.ShardedOptimizer: byte offsets to the peers' parameter buffers
         self._release_stream: torch.cuda.Stream | None = None
         self._release_fence_queued = False
 
@@ -158,6 +160,8 @@ class OptimiOptimizer(Optimizer):
                 kw = self._keywords(group)
                 if self._counts_steps:
                     kw["step"] = group["step"]
+                if self._peer_push is not None and self._supports_push:
+                    kw["_push"] = self._peer_push
                 if not params:
                     if self._counts_steps:
                         group["step"].add_(1)  # the reference advances the counter before looking at the lists
@@ -248,6 +252,7 @@ class Adam(OptimiOptimizer):
     """
 
     _functional = staticmethod(F.adam)
+    _supports_push = True
     _list_args = ("exp_avg", "exp_avg_sq", "kahan_comp")
     _state_arg_names = {"exp_avg": "exp_avgs", "exp_avg_sq": "exp_avg_sqs", "kahan_comp": "kahan_comps"}
     _scalar_keys = ("lr", "beta1", "beta2", "weight_decay", "eps", "decouple_wd", "decouple_lr", "max_lr")
@@ -309,6 +314,7 @@ class RAdam(Adam):
     """Rectified Adam (optimi/radam.py:57-71); same arguments as `Adam`."""
 
     _functional = staticmethod(F.radam)
+    _supports_push = False
 
 
 class Ranger(OptimiOptimizer):

@@ -11,12 +11,23 @@ reduced across ranks (that is the job of the data-parallel layer above the optim
 StableAdamW is the one optimizer with a per-tensor quantity (the RMS of g^2/v), so its ranges are
 cut on tensor boundaries instead and the exchange is one broadcast per owner of its (unequal) piece.
 
+Exchange modes (`exchange=`):
+    "nccl"   step the local range, then all-gather (works everywhere, any optimizer).
+    "push"   the flat buffers are symmetric-memory allocations mapped into every rank; the step kernel
+             itself stores each updated parameter vector into every peer's buffer over NVLink as it
+             goes (`optimi_b200_adam_push`), so the exchange overlaps the step tile by tile.  The
+             ranks then meet in a one-element all-reduce on the same stream, which orders every
+             rank's later work after all pushes.  Available for Adam/AdamW on CUDA; other optimizers
+             and CPU groups fall back to "nccl".
+    "auto"   "push" when available, else "nccl".
+
 Sharded and unsharded runs produce bit-identical parameters: each element sees exactly the same
 arithmetic, only on another GPU.
 """
 
 from __future__ import annotations
 
+import os
 from typing import Any, Callable
 
 import torch
@@ -82,7 +93,7 @@ class ShardedOptimizer:
     """
 
     def __init__(self, optimizer_cls: Callable, params, process_group=None, split_on_tensors: bool | None = None,
-                 gather: str | Callable = "nccl", **kwargs: Any):  # fmt: skip
+                 gather: str | Callable = "nccl", exchange: str = "nccl", **kwargs: Any):  # fmt: skip
         self.group = process_group
         self.rank = dist.get_rank(process_group) if dist.is_initialized() else 0
         self.world = dist.get_world_size(process_group) if dist.is_initialized() else 1
@@ -90,6 +101,15 @@ class ShardedOptimizer:
         if split_on_tensors is None:
             split_on_tensors = getattr(optimizer_cls, "__name__", "") == "StableAdamW"
         self.gather = gather
+        can_push = (
+            self.world > 1 and self.world <= 8 and getattr(optimizer_cls, "_supports_push", False) and not split_on_tensors
+            and all(p.is_cuda for p in self.params) and len({(p.device, p.dtype) for p in self.params}) == 1
+        )  # fmt: skip
+        if exchange == "push" and not can_push:
+            raise ValueError("exchange='push' needs 2-8 CUDA ranks, one dtype, and an optimizer with a push kernel (Adam, AdamW)")
+        self.exchange = "push" if (exchange in ("push", "auto") and can_push) else "nccl"
+        self._peer_deltas: list[int] | None = None
+        self._symm_handles = []
 
         # one flat buffer per (device, dtype)
         self.buckets: list[dict[str, Any]] = []
@@ -99,7 +119,10 @@ class ShardedOptimizer:
         shard_params: list[Tensor] = []
         for (device, dtype), plist in groups.items():
             layout = FlatLayout([p.numel() for p in plist], self.world, split_on_tensors)
-            flat = torch.zeros(layout.total, dtype=dtype, device=device)
+            if self.exchange == "push":
+                flat = self._symmetric_buffer(layout.total, dtype, device)
+            else:
+                flat = torch.zeros(layout.total, dtype=dtype, device=device)
             for p, off in zip(plist, layout.offsets):
                 view = flat[off : off + p.numel()].view(p.shape)
                 view.copy_(p.data)
@@ -113,6 +136,31 @@ class ShardedOptimizer:
             self.buckets.append(dict(layout=layout, flat=flat, params=plist, pieces=pieces, shards=shards))
         self.shard_params = shard_params
         self.inner = optimizer_cls(shard_params, **kwargs)
+        if self.exchange == "push":
+            self.inner._peer_push = self._peer_deltas
+            self._meet = torch.zeros(1, dtype=torch.int32, device=self.params[0].device)
+            # no rank may start pushing before every rank has finished filling its own buffer
+            torch.cuda.synchronize(self.params[0].device)
+            dist.barrier(self.group)
+
+    def _symmetric_buffer(self, numel: int, dtype: torch.dtype, device: torch.device) -> Tensor:
+        """A zeroed buffer every rank of the group can store into: torch symmetric memory (CUDA virtual
+        memory handles exchanged between the ranks).  Only plain peer stores are used on it."""
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm
+
+        flat = symm.empty(numel, dtype=dtype, device=device)
+        handle = symm.rendezvous(flat, self.group if self.group is not None else dist.group.WORLD)
+        flat.zero_()
+        base = flat.data_ptr()
+        ptrs = list(handle.buffer_ptrs)
+        if ptrs[self.rank] != base:
+            raise RuntimeError("symmetric memory: this rank's buffer pointer does not match the allocation")
+        self._peer_deltas = [ptrs[r] - base for r in range(self.world) if r != self.rank]
+        self._symm_handles.append(handle)
+        torch.cuda.synchronize(device)
+        dist.barrier(self.group)
+        return flat
 
     # convenience passthroughs ------------------------------------------------------------------
     @property
@@ -153,6 +201,11 @@ class ShardedOptimizer:
     def gather_params(self):
         """Hands every rank the updated parameters: one in-place all-gather per flat buffer."""
         if self.world == 1:
+            return
+        if self.exchange == "push":
+            # the step kernel already stored this rank's range into every peer; meeting in a tiny
+            # collective on the stream orders all later work after every rank's pushes
+            dist.all_reduce(self._meet, group=self.group)
             return
         for b in self.buckets:
             layout, flat = b["layout"], b["flat"]

@@ -18,7 +18,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, cname, kw, out):
+def _worker(rank, world, port, cname, kw, exchange, out):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
@@ -33,7 +33,8 @@ def _worker(rank, world, port, cname, kw, out):
         params = [torch.nn.Parameter(h.clone().to(dev)) for h in host]
         ref = [torch.nn.Parameter(h.clone().to(dev)) for h in host]
         cls = getattr(optimi_b200, cname)
-        sharded = ShardedOptimizer(cls, params, **kw)
+        sharded = ShardedOptimizer(cls, params, exchange=exchange, **kw)
+        assert sharded.exchange == exchange
         plain = cls(ref, **kw)
         for _ in range(5):
             grads = [(torch.randn(s, generator=g) * 1e-3).to(torch.bfloat16).to(dev) for s in shapes]
@@ -52,16 +53,21 @@ def _worker(rank, world, port, cname, kw, out):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("cname,kw", [("AdamW", dict(lr=3e-4, weight_decay=1e-5, decouple_lr=True)), ("StableAdamW", dict(lr=3e-4)),
-                                      ("Adan", dict(lr=3e-4, kahan_sum=True))])  # fmt: skip
-def test_sharded_step_equals_unsharded(cname, kw):
+@pytest.mark.parametrize("cname,kw,exchange", [
+    ("AdamW", dict(lr=3e-4, weight_decay=1e-5, decouple_lr=True), "nccl"),
+    ("AdamW", dict(lr=3e-4, weight_decay=1e-5, decouple_lr=True), "push"),
+    ("Adam", dict(lr=3e-4, weight_decay=1e-2, kahan_sum=False), "push"),
+    ("StableAdamW", dict(lr=3e-4), "nccl"),
+    ("Adan", dict(lr=3e-4, kahan_sum=True), "nccl"),
+])  # fmt: skip
+def test_sharded_step_equals_unsharded(cname, kw, exchange):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     world = 2
     ctx = mp.get_context("spawn")
     out = ctx.SimpleQueue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, cname, kw, out)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, cname, kw, exchange, out)) for r in range(world)]
     for p in procs:
         p.start()
     for p in procs:
