@@ -36,6 +36,10 @@ METRIC = "AdamW bf16-Kahan step: Gparams/s & HBM GB/s vs 8 TB/s, 8B shapes, 1/2/
 UNIT = "Gparams/s"
 BYTES_PER_PARAM = 18  # read p,g,m,v,k (10 B) + write p,m,v,k (8 B), bf16 + Kahan
 FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum per parameter of the AdamW bf16+Kahan kernel, from the ncu capture
+# of the 336 M-parameter case summarised in profiles/adamw_bf16_kahan_llama-0.3b_ncu_full.md; traffic is
+# proportional to the parameter count, so a launch's traffic is this figure times its elements
+NCU_DRAM_BYTES_PER_PARAM = 17.83
 
 HYPER = dict(lr=3e-4, betas=(0.9, 0.99), weight_decay=1e-5, eps=1e-6, decouple_lr=True)
 
@@ -388,15 +392,10 @@ def run_b200_arm(args):
         peak, peak_kind = FALLBACK_HBM_GBS, "fallback"
     kernel_launches_per_step = max(1, launches // args.steps)
     achieved = BYTES_PER_PARAM * n_local / (step_ms_max * 1e-3) / 1e9
-    traffic = None
-    traffic_path = os.path.join(ROOT, "profiles", "adamw_bf16_kahan_traffic.json")
-    if os.path.exists(traffic_path):
-        with open(traffic_path) as fh:
-            per_param = json.load(fh).get("dram_bytes_per_param")
-        if per_param:
-            traffic = per_param * n_local / kernel_launches_per_step
+    traffic = NCU_DRAM_BYTES_PER_PARAM * n_local / kernel_launches_per_step
     roofline = {
         "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": traffic,
+        "traffic_note": "bytes per launch: ncu dram read+write of a 336 M-param capture (17.83 B/param) scaled by elements per launch",
         "peak_kind": f"of {peak_kind}", "frac_of_8TBs": achieved / 8000.0, "kernel": "mta_kernel<bf16, AdamOp<kahan,update>>",
         "algorithmic_bytes_per_launch": BYTES_PER_PARAM * n_local / kernel_launches_per_step,
         "launches_per_step": kernel_launches_per_step,
