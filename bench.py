@@ -4,8 +4,10 @@
 
 One "step" is one optimizer step over the whole parameter list (synthetic, seeded; no dataset).
 Prints ONE JSON line (rank 0).  For N > 1 launch under torchrun; the optimizer states are sharded
-ZeRO-1 style (optimi_b200.zero.ShardedOptimizer): each rank steps 1/N of the elements, then an NCCL
-all-gather distributes the updated bf16 parameters — total work is fixed, so scaling is "strong".
+ZeRO-1 style (optimi_b200.zero.ShardedOptimizer): each rank steps 1/N of the elements and the updated
+bf16 parameters reach the other ranks either inside the step kernel (peer stores over NVLink,
+--exchange push, the default where available) or by an NCCL all-gather after it (--exchange nccl).
+Total work is fixed, so scaling is "strong".
 
 Keys beyond the driver's contract:
   roofline      dominant kernel against the HBM copy peak (MEASURED_PEAKS.json, else the fallback)
@@ -401,6 +403,13 @@ def run_b200_arm(args):
         "launches_per_step": kernel_launches_per_step,
     }  # fmt: skip
 
+    nvlink = None
+    if sharded is not None and sharded.exchange == "push":
+        # bytes this rank's step kernel stores into its peers, against the measured peer-copy rate of this pool
+        pushed = 2.0 * n_local * (world - 1)
+        nvlink = {"achieved": pushed / (step_ms_max * 1e-3) / 1e9, "peak": 770.0, "unit": "GB/s per direction per GPU",
+                  "frac": pushed / (step_ms_max * 1e-3) / 1e9 / 770.0, "bytes_pushed_per_rank_per_step": pushed}
+
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
         v, kind, cores, sample, _, _ = time_cpu_reference(args.workload, 12, 2, budget_s=20.0)
@@ -413,7 +422,7 @@ def run_b200_arm(args):
         "config": make_config(args.workload, world, args.exchange),
         "exchange": None if sharded is None else sharded.exchange,
         "hbm_gbs": achieved, "step_ms": step_ms_max, "gather_ms": gather_ms_max, "wall_ms_per_step": t_wall * 1e3 / args.steps,
-        "roofline": roofline, "cpu_baseline": cpu,
+        "roofline": roofline, "nvlink": nvlink, "cpu_baseline": cpu,
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
                 "ms_per_step": e2e_s * 1e3, "steps": e2e_steps},
         "gpu_launches": int(launches), "clocks": clocks.result, "library": os.path.relpath(_lib.LIB_PATH, ROOT),
