@@ -1,0 +1,123 @@
+"""Full-size checks on a B200: properties that do not need an oracle run at that size.
+
+1. Split invariance past 2^31 elements: the step is element-wise, so one 2.1 G-element tensor and the
+   same memory cut into a thousand uneven (partly misaligned) views must end bit-identical.  Exercises
+   64-bit offsets, the coarse block index, ragged tails and the scalar path at scale.
+2. More tensors than one by-value table holds (several launches per step) against the CPU oracle.
+3. BASELINE config 2 at full size (1.1 B-parameter Llama-style list, AdamW bf16 + Kahan, decouple_lr,
+   50 steps) against the unmodified reference's foreach path on the same GPU, bit for bit — runs only
+   where the reference package is present beside the repository (baseline/_ref).
+"""
+
+import os
+import sys
+import warnings
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _need_free(gb):
+    free, _ = torch.cuda.mem_get_info()
+    if free < gb * 2**30:
+        pytest.skip(f"needs {gb} GiB of free device memory")
+
+
+def test_split_invariance_beyond_two_to_the_31_elements():
+    import optimi_b200.functional as F
+
+    _need_free(60)
+    n = (1 << 31) + 4096 + 3
+    dt = torch.bfloat16
+    gen = torch.Generator(device="cuda").manual_seed(0)
+
+    def rnd(scale):
+        t = torch.empty(n, dtype=dt, device="cuda")
+        step = 1 << 27
+        for a in range(0, n, step):
+            b = min(n, a + step)
+            t[a:b] = torch.randn(b - a, device="cuda", generator=gen).mul_(scale).to(dt)
+        return t
+
+    base = [rnd(0.02), rnd(1e-3), rnd(1e-3), rnd(1e-6).abs_(), rnd(1e-5)]  # p g m v k
+    whole = [t.clone() for t in base]
+    parts = [t.clone() for t in base]
+    # cut points: some aligned to 8 elements, some not (those pieces take the scalar path)
+    cuts = sorted({0, n} | {int(x) for x in torch.randint(1, n - 1, (997,), generator=torch.Generator().manual_seed(1)).tolist()}
+                  | {1 << 20, (1 << 30) + 8, (1 << 31) - 1, (1 << 31) + 1})
+    views = [[t[a:b] for a, b in zip(cuts[:-1], cuts[1:])] for t in parts]
+
+    kw = dict(lr=3e-4, beta1=0.9, beta2=0.99, weight_decay=1e-5, eps=1e-6, decouple_wd=True, decouple_lr=True, max_lr=3e-4,
+              kahan_sum=True)  # fmt: skip
+    for s in range(2):
+        F.adam([whole[0]], [whole[1]], [whole[2]], [whole[3]], [whole[4]], step=torch.tensor(s, dtype=torch.int32), **kw)
+        F.adam(views[0], views[1], views[2], views[3], views[4], step=torch.tensor(s, dtype=torch.int32), **kw)
+    torch.cuda.synchronize()
+    for name, a, b, ref in zip("pgmvk", whole, parts, base):
+        assert torch.equal(a, b), f"{name}: split run differs from whole run"
+        if name != "g":
+            assert not torch.equal(a[-4096:], ref[-4096:]), f"{name}: tail was not updated"
+        else:
+            assert torch.equal(a, ref), "gradients must be left untouched"
+
+
+def test_more_tensors_than_one_table():
+    import optimi_b200
+    from oracle.port import OracleOptimizer
+
+    gen = torch.Generator().manual_seed(3)
+    sizes = [int(x) for x in torch.randint(1, 3000, (1500,), generator=gen)]
+    host = [(torch.randn(s, generator=gen) * 0.02).to(torch.bfloat16) for s in sizes]
+    grads = [[(torch.randn(s, generator=gen) * 1e-3).to(torch.bfloat16) for s in sizes] for _ in range(3)]
+    for name, cls, kw in [("adan", optimi_b200.Adan, dict(lr=3e-4, kahan_sum=True)), ("lion", optimi_b200.Lion, dict(lr=1e-4, weight_decay=0.1))]:
+        params = [h.clone().cuda().requires_grad_(True) for h in host]
+        opt = cls(params, **kw)
+        oracle = OracleOptimizer(name, [h.clone() for h in host], **kw)
+        for gs in grads:
+            for p, g in zip(params, gs):
+                p.grad = g.cuda()
+            opt.step()
+            oracle.step([g.clone() for g in gs])
+        torch.cuda.synchronize()
+        bad = [i for i, p in enumerate(params) if not torch.equal(p.detach().cpu(), oracle.params[i])]
+        assert not bad, f"{name}: tensors {bad[:10]} differ from the oracle"
+
+
+def test_config2_full_size_against_reference_foreach():
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_dir, "optimi")):
+        pytest.skip("reference package not present beside the repository")
+    _need_free(40)
+    sys.path.insert(0, ref_dir)
+    sys.path.insert(0, ROOT)
+    import optimi  # the unmodified reference
+
+    import optimi_b200
+    from bench import WORKLOADS, grad_scales, make_params
+
+    shapes = WORKLOADS["llama-1.1b"]()
+    hyper = dict(lr=3e-4, betas=(0.9, 0.99), weight_decay=1e-5, eps=1e-6, decouple_lr=True)
+    mine = [p.requires_grad_(True) for p in make_params(shapes, "cuda", torch.bfloat16, seed=0)]
+    theirs = [p.detach().clone().requires_grad_(True) for p in mine]
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        opt_ref = optimi.AdamW(theirs, foreach=True, triton=False, **hyper)
+    opt_b200 = optimi_b200.AdamW(mine, **hyper)
+    scales = grad_scales(len(shapes), seed=0)
+    for step in range(50):
+        gen = torch.Generator(device="cuda").manual_seed(1000 + step)
+        for p, q, sc in zip(mine, theirs, scales):
+            g = torch.randn(p.shape, device="cuda", generator=gen).mul_(sc).to(torch.bfloat16)
+            p.grad = g
+            q.grad = g.clone()  # the reference's foreach path clobbers its gradients
+        opt_b200.step()
+        opt_ref.step()
+    torch.cuda.synchronize()
+    for i, (p, q) in enumerate(zip(mine, theirs)):
+        assert torch.equal(p.detach(), q.detach()), f"param {i} {tuple(p.shape)} differs after 50 steps"
+        for key in ("exp_avg", "exp_avg_sq", "kahan_comp"):
+            assert torch.equal(opt_b200.state[p][key], opt_ref.state[q][key]), f"{key} of tensor {i} differs after 50 steps"
