@@ -32,15 +32,18 @@ constexpr int kBuckets = 256;       // coarse index over the tile range (see loc
 #endif
 constexpr int kTilesPerBlock = OPTIMI_TILES_PER_BLOCK;  // consecutive tiles one block walks through
 
-template <int NL>
+// SMALL = true is the few-tensor form (gradient release steps one parameter per launch): a table of a
+// few hundred bytes instead of ~30 KB keeps the launch itself cheap.
+template <int NL, bool SMALL = false>
 struct MtaTable {
-  static constexpr int CAP = kTableBytes / (NL * 8 + 12);
+  static constexpr int CAP = SMALL ? 4 : kTableBytes / (NL * 8 + 12);
+  static constexpr int NB = SMALL ? 4 : kBuckets;
   void* ptr[NL][CAP];       // ptr[list][tensor]
   long long numel[CAP];
   int tile_start[CAP + 1];  // prefix sum of blocks per tensor; tile_start[n_tensors] = grid size
   // bucket_tensor[b] = tensor that owns block (b << bucket_shift): a block starts its search there
   // and walks forward, which for lists of large tensors is zero or one step
-  int bucket_tensor[kBuckets];
+  int bucket_tensor[NB];
   int bucket_shift;
   int n_tensors;
   int tensor_base;          // index of tensor 0 of this table within the caller's whole list
@@ -160,8 +163,8 @@ struct Span {
 
 // `block_elems` = elements one block covers (kTilesPerBlock tiles).  s.len is the number of elements
 // of the tensor left from s.begin, capped at block_elems.
-template <int NL>
-__device__ __forceinline__ Span locate(const MtaTable<NL>& tab, int block, int block_elems) {
+template <class Table>
+__device__ __forceinline__ Span locate(const Table& tab, int block, int block_elems) {
   int t = tab.bucket_tensor[block >> tab.bucket_shift];
   while (tab.tile_start[t + 1] <= block) ++t;  // also skips empty tensors
   Span s;
@@ -175,8 +178,8 @@ __device__ __forceinline__ Span locate(const MtaTable<NL>& tab, int block, int b
 // Fetches the block's base pointers (advanced to the tile) and reports whether every present list
 // is 16-byte aligned there; tile offsets are multiples of 16 bytes, so only the tensors' base
 // addresses decide.
-template <typename T, int NL>
-__device__ __forceinline__ bool tile_pointers(const MtaTable<NL>& tab, const Span& s, T* (&p)[NL]) {
+template <typename T, int NL, class Table>
+__device__ __forceinline__ bool tile_pointers(const Table& tab, const Span& s, T* (&p)[NL]) {
   uintptr_t bits = 0;
 #pragma unroll
   for (int l = 0; l < NL; l++) {
@@ -291,14 +294,14 @@ __device__ __forceinline__ float scalar_elem(T* const (&p)[Op::NL], int i, const
 }
 
 // Processes the block's tile; returns this thread's share of the kSumSlot sum (0 without one).
-template <typename T, class Op>
-__device__ __forceinline__ double process_tile(const MtaTable<Op::NL>& tab, const typename Op::Args& args, Span& s) {
+template <typename T, class Op, class Table>
+__device__ __forceinline__ double process_tile(const Table& tab, const typename Op::Args& args, Span& s) {
   constexpr int V = VecN<T>::N;
   constexpr int U = Op::U;
   constexpr int TILE = kThreads * U * V;
   s = locate(tab, blockIdx.x, TILE * kTilesPerBlock);
   T* p[Op::NL];
-  const bool aligned = tile_pointers<T, Op::NL>(tab, s, p);
+  const bool aligned = tile_pointers<T, Op::NL, Table>(tab, s, p);
   const typename Op::Ctx ctx = Op::context(tab, s, args);
   double acc = 0.0;
   int done = 0;
@@ -338,8 +341,8 @@ constexpr int min_blocks() {
   return sizeof(T) == 2 && !__is_same(T, __nv_bfloat16) ? (Op::kMinBlocks > 2 ? Op::kMinBlocks - 2 : 1) : Op::kMinBlocks;
 }
 
-template <typename T, class Op>
-__global__ void __launch_bounds__(kThreads, min_blocks<T, Op>()) mta_kernel(const __grid_constant__ MtaTable<Op::NL> tab,
+template <typename T, class Op, bool SMALL>
+__global__ void __launch_bounds__(kThreads, min_blocks<T, Op>()) mta_kernel(const __grid_constant__ MtaTable<Op::NL, SMALL> tab,
                                                        const __grid_constant__ typename Op::Args args) {
   Span s;
   process_tile<T, Op>(tab, args, s);

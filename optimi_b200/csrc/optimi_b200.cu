@@ -69,9 +69,9 @@ static int check_lists(const char* name, int n, const int64_t* numels, int dtype
 
 // Walks the tensor list, filling one by-value table after another and handing each to `launch`.
 // `tile` = elements per block.
-template <int NL, class Launch>
+template <int NL, bool SMALL, class Launch>
 static int for_each_table(int n, const int64_t* numels, void* const* const (&lists)[NL], int tile, Launch&& launch) {
-  using Table = MtaTable<NL>;
+  using Table = MtaTable<NL, SMALL>;
   Table tab;  // ~30 KB on the host stack
   int i = 0, tile_base = 0;
   while (i < n) {
@@ -93,9 +93,9 @@ static int for_each_table(int n, const int64_t* numels, void* const* const (&lis
     tab.n_tensors = count;
     // coarse index: bucket b covers blocks [b << shift, (b+1) << shift)
     int shift = 0;
-    while ((tiles >> shift) >= kBuckets) shift++;
+    while ((tiles >> shift) >= Table::NB) shift++;
     tab.bucket_shift = shift;
-    for (int b = 0, t = 0; b < kBuckets; b++) {
+    for (int b = 0, t = 0; b < Table::NB; b++) {
       const long long first = (long long)b << shift;
       while (t + 1 < count && tab.tile_start[t + 1] <= first) t++;
       tab.bucket_tensor[b] = t;
@@ -116,8 +116,14 @@ constexpr int tile_of() { return kThreads * Op::U * VecN<T>::N * kTilesPerBlock;
 template <typename T, class Op>
 static int launch_op(const char* name, int n, const int64_t* numels, void* const* const (&lists)[Op::NL],
                      const typename Op::Args& args, cudaStream_t stream) {
-  return for_each_table<Op::NL>(n, numels, lists, tile_of<T, Op>(), [&](const MtaTable<Op::NL>& tab, int tiles) {
-    mta_kernel<T, Op><<<tiles, kThreads, 0, stream>>>(tab, args);
+  if (n <= MtaTable<Op::NL, true>::CAP) {  // few tensors (a gradient-release step): the small table
+    return for_each_table<Op::NL, true>(n, numels, lists, tile_of<T, Op>(), [&](const MtaTable<Op::NL, true>& tab, int tiles) {
+      mta_kernel<T, Op, true><<<tiles, kThreads, 0, stream>>>(tab, args);
+      return check_launch(name);
+    });
+  }
+  return for_each_table<Op::NL, false>(n, numels, lists, tile_of<T, Op>(), [&](const MtaTable<Op::NL, false>& tab, int tiles) {
+    mta_kernel<T, Op, false><<<tiles, kThreads, 0, stream>>>(tab, args);
     return check_launch(name);
   });
 }
@@ -150,8 +156,8 @@ static int dispatch(const char* name, int dtype, bool kahan, bool update, int n,
 // Pass A with the per-tile sum: advances both averages and writes the tile's sum of
 // g^2 / max(v, eps^2) to partial[tile] — one double per tile, written (not accumulated), so the
 // scratch needs no clearing and the result does not depend on block scheduling.
-template <typename T>
-__global__ void __launch_bounds__(kThreads, 10) stable_moments_sum_kernel(const __grid_constant__ MtaTable<4> tab,
+template <typename T, bool SMALL>
+__global__ void __launch_bounds__(kThreads, 10) stable_moments_sum_kernel(const __grid_constant__ MtaTable<4, SMALL> tab,
                                                                       const __grid_constant__ StableMomentsArgs a,
                                                                       double* __restrict__ partial) {
   Span s;
@@ -177,8 +183,8 @@ struct StableFinalizeArgs {
 // One block per tensor: folds the tensor's tile partials in a fixed order, then does on the device
 // what the reference does on the host after `.item()` (optimi/stableadamw.py:512-524): mean and
 // square root rounded to the storage type, -lr / max(1, rms) and the weight-decay factor in double.
-template <typename T>
-__global__ void __launch_bounds__(256) stable_finalize_kernel(const __grid_constant__ MtaTable<4> tab,
+template <typename T, bool SMALL>
+__global__ void __launch_bounds__(256) stable_finalize_kernel(const __grid_constant__ MtaTable<4, SMALL> tab,
                                                               const __grid_constant__ StableFinalizeArgs a,
                                                               const double* __restrict__ partial,
                                                               float2* __restrict__ tensor_scalars) {
@@ -253,13 +259,17 @@ static int stableadamw_typed(int n, void* const* params, void* const* grads, voi
   fa.max_lr = max_lr;
   fa.decouple_lr = decouple_lr;
 
-  int rc = for_each_table<4>(n, numels, lists_a, tile_a, [&](const MtaTable<4>& tab, int tiles) {
-    stable_moments_sum_kernel<T><<<tiles, kThreads, 0, stream>>>(tab, ma, partial);
-    int r = check_launch("optimi_b200_stableadamw (moments)");
-    if (r != OPTIMI_OK) return r;
-    stable_finalize_kernel<T><<<tab.n_tensors, 256, 0, stream>>>(tab, fa, partial, tensor_scalars);
-    return check_launch("optimi_b200_stableadamw (finalize)");
-  });
+  auto pass_a = [&](auto small) {
+    constexpr bool SMALL = decltype(small)::value;
+    return for_each_table<4, SMALL>(n, numels, lists_a, tile_a, [&](const MtaTable<4, SMALL>& tab, int tiles) {
+      stable_moments_sum_kernel<T, SMALL><<<tiles, kThreads, 0, stream>>>(tab, ma, partial);
+      int r = check_launch("optimi_b200_stableadamw (moments)");
+      if (r != OPTIMI_OK) return r;
+      stable_finalize_kernel<T, SMALL><<<tab.n_tensors, 256, 0, stream>>>(tab, fa, partial, tensor_scalars);
+      return check_launch("optimi_b200_stableadamw (finalize)");
+    });
+  };
+  int rc = n <= MtaTable<4, true>::CAP ? pass_a(std::true_type{}) : pass_a(std::false_type{});
   if (rc != OPTIMI_OK) return rc;
 
   StableUpdateArgs ua;

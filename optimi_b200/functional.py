@@ -13,54 +13,22 @@ values the kernels receive are the ones the reference's ATen ops receive.
 
 from __future__ import annotations
 
-import math
+import ctypes
 
 import torch
 from torch import Tensor
 
 from . import _lib
-from ._launch import TensorList, as_list, launch
+from . import _tails as T
+from ._launch import TensorList, launch
+from ._tails import debias, debias_beta  # noqa: F401  (part of the reference's utils API)
 
 __all__ = ["adam", "adamw", "lion", "sgd", "stableadamw", "adan", "radam", "ranger", "debias", "debias_beta"]
-
-
-def debias(beta: float, step: int) -> float:
-    """Adam's bias-correction denominator 1 - beta^step (optimi/utils.py:26-28)."""
-    return 1 - beta**step
-
-
-def debias_beta(beta: float, step: int) -> float:
-    """Beta with the bias correction folded in, beta*(1-beta^(step-1))/(1-beta^step) in the
-    reference's simplified form (optimi/utils.py:31-36); 0 at step 1."""
-    return (beta**step - beta) / (beta**step - 1)
 
 
 def _advance(step: Tensor) -> int:
     step.add_(1)
     return int(step.item())
-
-
-def _fold_weight_decay(weight_decay: float, lr: float, decouple_wd: bool, decouple_lr: bool, max_lr: float | None) -> float:
-    """The multiplicative factor for (fully) decoupled decay, or the raw L2 coefficient."""
-    if weight_decay != 0:
-        if decouple_lr:
-            return 1 - (lr / max_lr) * weight_decay
-        if decouple_wd:
-            return 1 - lr * weight_decay
-    return weight_decay
-
-
-def _rectification(beta2: float, step: int) -> float | None:
-    """RAdam's variance rectification term; None while the SMA length is at most 5."""
-    rho_inf = 2 / (1 - beta2) - 1
-    rho = rho_inf - 2 * step * (beta2**step) / debias(beta2, step)
-    if rho > 5:
-        return math.sqrt(((rho - 4) * (rho - 2) * rho_inf) / ((rho_inf - 4) * (rho_inf - 2) * rho))
-    return None
-
-
-def _kahan(kahan_sum: bool, kahan_comps) -> bool:
-    return bool(kahan_sum) and kahan_comps is not None
 
 
 def adam(
@@ -94,27 +62,18 @@ def adam(
     fused step + exchange kernel of a sharded run; see `optimi_b200.zero.ShardedOptimizer`.
     """
     t = _advance(step)
-    beta1_comp = 1 - debias_beta(beta1, t)
-    beta2_hat = debias_beta(beta2, t)
-    beta2_comp = 1 - beta2_hat
-    wd = _fold_weight_decay(weight_decay, lr, decouple_wd, decouple_lr, max_lr)
+    tail = T.adam_tail(t, not optimizer_accumulation, lr=lr, beta1=beta1, beta2=beta2, weight_decay=weight_decay, eps=eps,
+                       decouple_wd=decouple_wd, decouple_lr=decouple_lr, max_lr=max_lr, kahan_sum=kahan_sum)  # fmt: skip
+    lists = [params, grads, exp_avgs, exp_avg_sqs, kahan_comps]
+    names = ("params", "grads", "exp_avgs", "exp_avg_sqs", "kahan_comps")
     if _push is not None and not optimizer_accumulation:
         import ctypes
 
         deltas = (ctypes.c_int64 * len(_push))(*_push)
-        tail = (lr, beta1_comp, beta2_hat, beta2_comp, wd, eps, int(decouple_wd or decouple_lr), int(bool(kahan_sum)),
-                len(_push), ctypes.cast(deltas, ctypes.c_void_p))  # fmt: skip
-        launch(
-            "optimi_b200_adam_push", [params, grads, exp_avgs, exp_avg_sqs, kahan_comps],
-            ("params", "grads", "exp_avgs", "exp_avg_sqs", "kahan_comps"), lambda *_: tail, _stream, _trusted,
-        )  # fmt: skip
+        push_tail = tail[:-1] + (len(_push), ctypes.cast(deltas, ctypes.c_void_p))
+        launch("optimi_b200_adam_push", lists, names, lambda *_: push_tail, _stream, _trusted)
         return
-    tail = (lr, beta1_comp, beta2_hat, beta2_comp, wd, eps, int(decouple_wd or decouple_lr), int(bool(kahan_sum)),
-            int(not optimizer_accumulation))  # fmt: skip
-    launch(
-        "optimi_b200_adam", [params, grads, exp_avgs, exp_avg_sqs, kahan_comps],
-        ("params", "grads", "exp_avgs", "exp_avg_sqs", "kahan_comps"), lambda *_: tail, _stream, _trusted,
-    )  # fmt: skip
+    launch("optimi_b200_adam", lists, names, lambda *_: tail, _stream, _trusted)
 
 
 def adamw(
@@ -170,8 +129,8 @@ def lion(
     _trusted: bool = False,
 ):
     """Lion step.  Weight decay is always decoupled (optimi/lion.py:227-231)."""
-    wd = _fold_weight_decay(weight_decay, lr, True, decouple_lr, max_lr)
-    tail = (lr, 1 - beta1, 1 - beta2, wd, int(bool(kahan_sum)), int(not optimizer_accumulation))
+    tail = T.lion_tail(0, not optimizer_accumulation, lr=lr, beta1=beta1, beta2=beta2, weight_decay=weight_decay,
+                       decouple_lr=decouple_lr, max_lr=max_lr, kahan_sum=kahan_sum)  # fmt: skip
     launch("optimi_b200_lion", [params, grads, exp_avgs, kahan_comps], ("params", "grads", "exp_avgs", "kahan_comps"),
            lambda *_: tail, _stream, _trusted)  # fmt: skip
 
@@ -198,11 +157,10 @@ def sgd(
     _trusted: bool = False,
 ):
     """SGD step with optional momentum, dampening and (decoupled) weight decay."""
-    wd = _fold_weight_decay(weight_decay, lr, decouple_wd, decouple_lr, max_lr)
     if momentum == 0:
         exp_avgs = None
-    tail = (lr, momentum, wd, int(bool(dampening)), int(decouple_wd or decouple_lr), int(bool(kahan_sum)),
-            int(not optimizer_accumulation))  # fmt: skip
+    tail = T.sgd_tail(0, not optimizer_accumulation, lr=lr, momentum=momentum, weight_decay=weight_decay, dampening=dampening,
+                      decouple_wd=decouple_wd, decouple_lr=decouple_lr, max_lr=max_lr, kahan_sum=kahan_sum)  # fmt: skip
     launch("optimi_b200_sgd", [params, grads, exp_avgs, kahan_comps], ("params", "grads", "exp_avgs", "kahan_comps"),
            lambda *_: tail, _stream, _trusted)  # fmt: skip
 
@@ -219,6 +177,14 @@ def _stable_workspace(device: torch.device, stream_id: int, nbytes: int) -> Tens
         ws = torch.empty(max(nbytes, 1 << 16), dtype=torch.uint8, device=device)
         _workspaces[key] = ws
     return ws
+
+
+def stable_workspace_args(device: torch.device, stream_ptr: int, params) -> tuple:
+    """(pointer, size) of the cached scratch StableAdamW's reduction needs for this tensor list."""
+    numels = _lib.numel_array(params)
+    need = _lib.LIB.optimi_b200_stableadamw_workspace_bytes(len(params), ctypes.cast(numels, ctypes.c_void_p))
+    ws = _stable_workspace(device, stream_ptr, need)
+    return (ctypes.c_void_p(ws.data_ptr()), ws.numel())
 
 
 def stableadamw(
@@ -248,24 +214,16 @@ def stableadamw(
 ):
     """StableAdamW step.  `eps_sqs` and `mean_squares` are accepted for signature compatibility; the
     kernels derive eps^2 from `eps` and keep the per-tensor mean square in their own scratch."""
-    import ctypes
-
     t = _advance(step)
-    beta1_comp = 1 - debias_beta(beta1, t)
-    beta2_hat = debias_beta(beta2, t)
-    beta2_comp = 1 - beta2_hat
     update = not optimizer_accumulation
+    scalars = T.stableadamw_tail(t, update, lr=lr, beta1=beta1, beta2=beta2, weight_decay=weight_decay, eps=eps,
+                                 decouple_lr=decouple_lr, max_lr=max_lr, kahan_sum=kahan_sum)  # fmt: skip
 
     def tail(device, dtype, sub):
-        ws_ptr, ws_bytes = None, 0
-        if update:
-            numels = _lib.numel_array(sub[0])
-            need = _lib.LIB.optimi_b200_stableadamw_workspace_bytes(len(sub[0]), ctypes.cast(numels, ctypes.c_void_p))
-            s = _stream if _stream is not None else torch.cuda.current_stream(device)
-            ws = _stable_workspace(device, s.cuda_stream, need)
-            ws_ptr, ws_bytes = ctypes.c_void_p(ws.data_ptr()), ws.numel()
-        return (lr, beta1_comp, beta2_hat, beta2_comp, weight_decay, eps, int(bool(decouple_lr)),
-                float(max_lr) if max_lr is not None else 0.0, int(bool(kahan_sum)), int(update), ws_ptr, ws_bytes)  # fmt: skip
+        if not update:
+            return scalars + (None, 0)
+        s = _stream if _stream is not None else torch.cuda.current_stream(device)
+        return scalars + stable_workspace_args(device, s.cuda_stream, sub[0])
 
     launch(
         "optimi_b200_stableadamw", [params, grads, exp_avgs, exp_avg_sqs, kahan_comps],
@@ -302,16 +260,8 @@ def adan(
 ):
     """Adan step.  `prev_grads` holds the negated previous gradient."""
     t = _advance(step)
-    beta1_comp = 1 - debias_beta(beta1, t)
-    beta2_comp = 1 - debias_beta(beta2, t)
-    beta3_hat = debias_beta(beta3, t)
-    beta3_comp = 1 - beta3_hat
-    wd = weight_decay
-    if wd != 0:
-        wd = (lr / max_lr) * wd if decouple_lr else lr * wd
-        wd = 1 - wd if adam_wd else 1 + wd
-    tail = (lr, beta1_comp, beta2, beta2_comp, beta3_hat, beta3_comp, eps, wd, int(bool(adam_wd)), int(bool(kahan_sum)),
-            int(not optimizer_accumulation))  # fmt: skip
+    tail = T.adan_tail(t, not optimizer_accumulation, lr=lr, beta1=beta1, beta2=beta2, beta3=beta3, weight_decay=weight_decay,
+                       eps=eps, decouple_lr=decouple_lr, max_lr=max_lr, adam_wd=adam_wd, kahan_sum=kahan_sum)  # fmt: skip
     launch(
         "optimi_b200_adan", [params, grads, exp_avgs, exp_avg_diffs, exp_avg_sqs, prev_grads, kahan_comps],
         ("params", "grads", "exp_avgs", "exp_avg_diffs", "exp_avg_sqs", "prev_grads", "kahan_comps"), lambda *_: tail, _stream, _trusted,
@@ -344,13 +294,8 @@ def radam(
 ):
     """RAdam step: Adam averages with a rectified step once the variance estimate is trusted."""
     t = _advance(step)
-    beta1_comp = 1 - debias_beta(beta1, t)
-    beta2_hat = debias_beta(beta2, t)
-    beta2_comp = 1 - beta2_hat
-    rect = _rectification(beta2, t)
-    wd = _fold_weight_decay(weight_decay, lr, decouple_wd, decouple_lr, max_lr)
-    tail = (lr, beta1_comp, beta2_hat, beta2_comp, wd, eps, int(rect is not None), rect if rect is not None else 0.0,
-            int(decouple_wd or decouple_lr), int(bool(kahan_sum)), int(not optimizer_accumulation))  # fmt: skip
+    tail = T.radam_tail(t, not optimizer_accumulation, lr=lr, beta1=beta1, beta2=beta2, weight_decay=weight_decay, eps=eps,
+                        decouple_wd=decouple_wd, decouple_lr=decouple_lr, max_lr=max_lr, kahan_sum=kahan_sum)  # fmt: skip
     launch(
         "optimi_b200_radam", [params, grads, exp_avgs, exp_avg_sqs, kahan_comps],
         ("params", "grads", "exp_avgs", "exp_avg_sqs", "kahan_comps"), lambda *_: tail, _stream, _trusted,
@@ -386,13 +331,8 @@ def ranger(
 ):
     """Ranger step: RAdam followed, on every k-th step, by a Lookahead pull toward the slow weights."""
     t = _advance(step)
-    beta1_comp = 1 - debias_beta(beta1, t)
-    beta2_hat = debias_beta(beta2, t)
-    beta2_comp = 1 - beta2_hat
-    rect = _rectification(beta2, t)
-    wd = _fold_weight_decay(weight_decay, lr, decouple_wd, decouple_lr, max_lr)
-    tail = (lr, beta1_comp, beta2_hat, beta2_comp, wd, eps, int(rect is not None), rect if rect is not None else 0.0,
-            int(t % k == 0), alpha, int(decouple_wd or decouple_lr), int(bool(kahan_sum)), int(not optimizer_accumulation))  # fmt: skip
+    tail = T.ranger_tail(t, not optimizer_accumulation, lr=lr, beta1=beta1, beta2=beta2, weight_decay=weight_decay, eps=eps,
+                         k=k, alpha=alpha, decouple_wd=decouple_wd, decouple_lr=decouple_lr, max_lr=max_lr, kahan_sum=kahan_sum)  # fmt: skip
     launch(
         "optimi_b200_ranger", [params, grads, exp_avgs, exp_avg_sqs, la_params, kahan_comps],
         ("params", "grads", "exp_avgs", "exp_avg_sqs", "la_params", "kahan_comps"), lambda *_: tail, _stream, _trusted,

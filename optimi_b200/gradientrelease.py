@@ -27,8 +27,10 @@ class _ReleaseHook:
         self.optimizer = optimizer
 
     def __call__(self, param: Tensor) -> None:
-        self.optimizer.step(param=param)
-        self.optimizer.zero_grad(param=param)
+        # what the reference's hook does — optimizer.step(param=param); optimizer.zero_grad(param=param)
+        # (optimi/gradientrelease.py:13-15) — without the two method-call wrappers
+        self.optimizer._release(param)
+        param.grad = None
 
 
 def prepare_for_gradient_release(model: Module, optimizer: OptimiOptimizer, ignore_existing_hooks: bool = False):

@@ -18,7 +18,12 @@ import torch
 from torch import Tensor
 from torch.optim.optimizer import Optimizer
 
+import ctypes
+
+from . import _lib
+from . import _tails as T
 from . import functional as F
+from ._launch import _dense_like
 
 LOW_PRECISION = (torch.float16, torch.bfloat16)
 
@@ -26,6 +31,40 @@ LOW_PRECISION = (torch.float16, torch.bfloat16)
 def _check_range(name: str, value: float, shown: str | None = None):
     if not 0.0 <= value < 1.0:
         raise ValueError(f"Invalid {name} parameter: {shown or name}={value}")
+
+
+class _ReleasePlan:
+    """Prebuilt C arguments for stepping one parameter (gradient release).  Valid while the parameter
+    and its state tensors stay where they are; only the gradient pointer changes from call to call."""
+
+    __slots__ = ("fn_name", "fn", "group", "device", "index", "dtype_code", "tensors", "addresses", "arrays", "args",
+                 "grad_slot", "numels", "numels_arg", "step_view")  # fmt: skip
+
+    def __init__(self, fn_name: str, param: Tensor, group: dict, states: list, step: Tensor | None):
+        self.fn_name, self.fn, self.group = fn_name, getattr(_lib.LIB, fn_name), group
+        self.device, self.index = param.device, param.device.index
+        self.dtype_code = _lib.DTYPE_CODE[param.dtype]
+        self.tensors = [param] + states
+        for t in states:
+            if t is not None and (t.device != param.device or t.dtype != param.dtype or t.numel() != param.numel() or not _dense_like(t, param)):
+                raise RuntimeError(f"{fn_name}: a state tensor does not match its parameter's dtype, device, size or layout")
+        self.addresses = [None if t is None else t.data_ptr() for t in self.tensors]
+        # C order: params, grads, states...
+        self.grad_slot = (ctypes.c_void_p * 1)(0)
+        self.arrays = [(ctypes.c_void_p * 1)(self.addresses[0]), self.grad_slot] + [
+            None if a is None else (ctypes.c_void_p * 1)(a) for a in self.addresses[1:]
+        ]
+        self.args = [None if a is None else ctypes.cast(a, ctypes.c_void_p) for a in self.arrays]
+        self.numels = (ctypes.c_int64 * 1)(param.numel())
+        self.numels_arg = ctypes.cast(self.numels, ctypes.c_void_p)
+        # the int32 CPU counter of the checkpoint layout, advanced in place through a numpy view
+        self.step_view = None if step is None else step.numpy()
+
+    def fresh(self, param: Tensor) -> bool:
+        for t, a in zip(self.tensors, self.addresses):
+            if (None if t is None else t.data_ptr()) != a:
+                return False
+        return True
 
 
 class OptimiOptimizer(Optimizer):
@@ -37,6 +76,10 @@ class OptimiOptimizer(Optimizer):
     _state_arg_names: dict[str, str] = {}  # state key -> functional keyword
     _counts_steps = True  # keeps a `step` counter (Lion and SGD do not)
     _supports_push = False  # has a fused step + peer-push kernel (sharded runs)
+    _c_fn: str = ""  # C entry point
+    _c_states: tuple[str, ...] = ()  # state keys in the order of the C signature (after params, grads)
+    _tail: Callable = None  # host scalars -> C arguments (optimi_b200._tails)
+    _needs_workspace = False
     _scalar_keys: tuple[str, ...] = ()  # param_group keys forwarded as keywords
 
     def __init__(self, params: Iterable[Tensor] | Iterable[dict], defaults: dict[str, Any]):
@@ -73,6 +116,8 @@ class OptimiOptimizer(Optimizer):
 
         self._optimizer_accumulation = False
         self._peer_push: list[int] | None = None  # set by zero.ShardedOptimizer: byte offsets to the peers' parameter buffers
+        self._plans: dict[Tensor, _ReleasePlan] = {}  # gradient release: cached C arguments per parameter
+        self._tail_cache: dict[int, tuple] = {}  # id(group) -> (key, tail): scalars are shared by a group's parameters
         self._release_stream: torch.cuda.Stream | None = None
         self._release_fence_queued = False
 
@@ -171,21 +216,67 @@ class OptimiOptimizer(Optimizer):
                     kahan_sum=group["kahan_sum"], gradient_release=False, optimizer_accumulation=False, _trusted=True,
                 )  # fmt: skip
         else:
-            state = self.state[param]
-            group = state["group"]
-            self._init_state(group, state, param)
-            kw = self._keywords(group)
-            if self._counts_steps:
-                kw["step"] = state["step"]
-            stream = self._enter_release_stream(param)
-            type(self)._functional(
-                param, param.grad, **{self._state_arg_names[k]: state[k] for k in self._list_args}, **kw,
-                kahan_sum=group["kahan_sum"], gradient_release=True, optimizer_accumulation=self._optimizer_accumulation,
-                _stream=stream, _trusted=True,
-            )  # fmt: skip
-            if stream is not None:
-                param.grad.record_stream(stream)
+            self._release(param)
         return loss
+
+    # ---- gradient release: the per-parameter step ------------------------------------------------
+    def _release(self, param: Tensor) -> None:
+        """Steps one parameter from its gradient (the body of `step(param=...)` and of the hook).
+
+        This runs once per parameter per backward pass on the autograd thread, where every
+        microsecond delays the enqueueing of the backward pass itself, so it is kept lean: the
+        C arguments are prebuilt per parameter (`_ReleasePlan`), the host scalars are computed once
+        per (group, step count) and shared by the group's parameters, the step counter tensor is
+        advanced through a numpy view, and the launch goes straight to the C entry point.
+        Semantics are those of the reference's `step(param=...)` (optimi/adam.py:183-208): lazy state
+        creation, a per-parameter step counter that also advances on accumulation micro-steps.
+        """
+        plan = self._plans.get(param)
+        if plan is None or not plan.fresh(param):
+            plan = self._plans[param] = self._make_plan(param)
+        grad = param.grad
+        if grad.dtype != param.dtype or not _dense_like(grad, param):
+            raise RuntimeError(f"{plan.fn_name}: the gradient does not match its parameter's dtype or layout")
+        plan.grad_slot[0] = grad.data_ptr()
+
+        t = 0
+        if plan.step_view is not None:
+            plan.step_view += 1
+            t = int(plan.step_view)
+        update = not self._optimizer_accumulation
+        group = plan.group
+        key = (t, update, group["kahan_sum"], *[group[k] for k in self._scalar_keys])
+        cached = self._tail_cache.get(id(group))
+        if cached is not None and cached[0] == key:
+            tail = cached[1]
+        else:
+            tail = type(self)._tail(t, update, kahan_sum=group["kahan_sum"], **{k: group[k] for k in self._scalar_keys})
+            self._tail_cache[id(group)] = (key, tail)
+
+        side = self._enter_release_stream(param)
+        stream_ptr = side.cuda_stream if side is not None else torch._C._cuda_getCurrentRawStream(plan.index)
+        if self._needs_workspace:
+            tail = tail + (F.stable_workspace_args(plan.device, stream_ptr, (param,)) if update else (None, 0))
+        if torch._C._cuda_getDevice() == plan.index:
+            rc = plan.fn(1, *plan.args, plan.numels_arg, plan.dtype_code, *tail, stream_ptr)
+        else:
+            with torch.cuda.device(plan.device):
+                rc = plan.fn(1, *plan.args, plan.numels_arg, plan.dtype_code, *tail, stream_ptr)
+        if rc != 0:
+            _lib.check(rc)
+        if side is not None:
+            grad.record_stream(side)
+
+    def _make_plan(self, param: Tensor) -> "_ReleasePlan":
+        state = self.state[param]
+        group = state["group"]
+        with torch.no_grad():
+            self._init_state(group, state, param)
+        if not param.is_cuda:
+            raise RuntimeError(f"{self._c_fn}: parameters live on {param.device}; optimi_b200 steps CUDA tensors only (there is no CPU path)")
+        if param.dtype not in _lib.DTYPE_CODE:
+            raise RuntimeError(f"{self._c_fn}: unsupported parameter dtype {param.dtype} (float32, bfloat16 and float16 are)")
+        return _ReleasePlan(self._c_fn, param, group, [state[k] for k in self._c_states], state.get("step") if self._counts_steps else None)
 
     # ---- gradient release on a side stream ----------------------------------------------------
     def use_release_stream(self, stream: torch.cuda.Stream | bool | None = True) -> None:
@@ -252,6 +343,7 @@ class Adam(OptimiOptimizer):
     """
 
     _functional = staticmethod(F.adam)
+    _c_fn, _c_states, _tail = "optimi_b200_adam", ("exp_avg", "exp_avg_sq", "kahan_comp"), staticmethod(T.adam_tail)
     _supports_push = True
     _list_args = ("exp_avg", "exp_avg_sq", "kahan_comp")
     _state_arg_names = {"exp_avg": "exp_avgs", "exp_avg_sq": "exp_avg_sqs", "kahan_comp": "kahan_comps"}
@@ -314,6 +406,7 @@ class RAdam(Adam):
     """Rectified Adam (optimi/radam.py:57-71); same arguments as `Adam`."""
 
     _functional = staticmethod(F.radam)
+    _c_fn, _tail = "optimi_b200_radam", staticmethod(T.radam_tail)
     _supports_push = False
 
 
@@ -322,6 +415,7 @@ class Ranger(OptimiOptimizer):
     Weight decay is decoupled by default."""
 
     _functional = staticmethod(F.ranger)
+    _c_fn, _c_states, _tail = "optimi_b200_ranger", ("exp_avg", "exp_avg_sq", "la_param", "kahan_comp"), staticmethod(T.ranger_tail)
     _list_args = ("exp_avg", "exp_avg_sq", "la_param", "kahan_comp")
     _state_arg_names = {"exp_avg": "exp_avgs", "exp_avg_sq": "exp_avg_sqs", "la_param": "la_params", "kahan_comp": "kahan_comps"}
     _scalar_keys = ("lr", "beta1", "beta2", "weight_decay", "eps", "k", "alpha", "decouple_wd", "decouple_lr", "max_lr")
@@ -363,6 +457,7 @@ class Lion(OptimiOptimizer):
     """Lion, evolved sign momentum (optimi/lion.py:56-68).  Weight decay is always decoupled."""
 
     _functional = staticmethod(F.lion)
+    _c_fn, _c_states, _tail = "optimi_b200_lion", ("exp_avg", "kahan_comp"), staticmethod(T.lion_tail)
     _list_args = ("exp_avg", "kahan_comp")
     _state_arg_names = {"exp_avg": "exp_avgs", "kahan_comp": "kahan_comps"}
     _counts_steps = False
@@ -397,6 +492,7 @@ class SGD(OptimiOptimizer):
     `torch_init=True` seeds the momentum buffer with the first gradient when dampening."""
 
     _functional = staticmethod(F.sgd)
+    _c_fn, _c_states, _tail = "optimi_b200_sgd", ("exp_avg", "kahan_comp"), staticmethod(T.sgd_tail)
     _list_args = ("exp_avg", "kahan_comp")
     _state_arg_names = {"exp_avg": "exp_avgs", "kahan_comp": "kahan_comps"}
     _counts_steps = False
@@ -443,6 +539,8 @@ class StableAdamW(OptimiOptimizer):
     (optimi/stableadamw.py:76-89).  The RMS is reduced on the device; a step never synchronises."""
 
     _functional = staticmethod(F.stableadamw)
+    _c_fn, _c_states, _tail = "optimi_b200_stableadamw", ("exp_avg", "exp_avg_sq", "kahan_comp"), staticmethod(T.stableadamw_tail)
+    _needs_workspace = True
     _list_args = ("exp_avg", "exp_avg_sq", "eps_sq", "kahan_comp")
     _state_arg_names = {"exp_avg": "exp_avgs", "exp_avg_sq": "exp_avg_sqs", "eps_sq": "eps_sqs", "kahan_comp": "kahan_comps"}
     _scalar_keys = ("lr", "beta1", "beta2", "weight_decay", "eps", "decouple_lr", "max_lr")
@@ -483,6 +581,8 @@ class Adan(OptimiOptimizer):
     reference it does not forward `adam_wd` to the functional step (optimi/adan.py:181-231)."""
 
     _functional = staticmethod(F.adan)
+    _c_fn, _c_states, _tail = ("optimi_b200_adan", ("exp_avg", "exp_avg_diff", "exp_avg_sq", "prev_grad", "kahan_comp"),
+                               staticmethod(T.adan_tail))  # fmt: skip
     _list_args = ("exp_avg", "exp_avg_diff", "exp_avg_sq", "prev_grad", "kahan_comp")
     _state_arg_names = {"exp_avg": "exp_avgs", "exp_avg_diff": "exp_avg_diffs", "exp_avg_sq": "exp_avg_sqs",
                         "prev_grad": "prev_grads", "kahan_comp": "kahan_comps"}  # fmt: skip

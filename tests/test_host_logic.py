@@ -9,6 +9,7 @@ import torch
 from torch import nn
 
 import optimi_b200
+from optimi_b200 import _tails as T
 from optimi_b200 import functional as F
 
 ALL = [optimi_b200.Adam, optimi_b200.AdamW, optimi_b200.Adan, optimi_b200.Lion, optimi_b200.RAdam, optimi_b200.Ranger,
@@ -153,9 +154,9 @@ def test_debias_beta_matches_closed_form():
 
 
 def test_rectification_switches_on_at_step_six_for_beta2_099():
-    assert [F._rectification(0.99, t) is not None for t in range(1, 9)] == [False] * 5 + [True] * 3
+    assert [T.rectification(0.99, t) is not None for t in range(1, 9)] == [False] * 5 + [True] * 3
     rho_inf = 2 / (1 - 0.99) - 1
-    assert 0 < F._rectification(0.99, 6) < 1 and abs(F._rectification(0.99, 10**6) - 1) < 1e-3 and rho_inf > 5
+    assert 0 < T.rectification(0.99, 6) < 1 and abs(T.rectification(0.99, 10**6) - 1) < 1e-3 and rho_inf > 5
 
 
 def test_param_groups_weight_decay():
