@@ -430,17 +430,129 @@ def run_b200_arm(args):
     print(json.dumps(line))
 
 
+# ------------------------------------------------------------------------------------------------
+# secondary workload: gradient release + optimizer accumulation inside a real backward pass
+# ------------------------------------------------------------------------------------------------
+def run_gradient_release(args):
+    """BASELINE config 5: 24-layer GPT-style decoder (d_model 1024, 16 heads, FFN 4096, vocab 50304, bf16, 388
+    parameter tensors), random token ids at batch 8 x seq 1024, AdamW + Kahan stepping from backward hooks with
+    4-step optimizer accumulation.  Reports device milliseconds per micro-step (forward + backward + released
+    steps) for: no optimizer at all, optimi_b200 hooks on the backward stream, optimi_b200 hooks on a side stream,
+    and the reference's hooks with its Triton and ATen back ends when the reference package is present."""
+    import warnings
+
+    import torch.nn as nn
+    import torch.nn.functional as Fn
+
+    import optimi_b200
+
+    warnings.simplefilter("ignore")
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    optimi = None
+    if os.path.isdir(os.path.join(ref_dir, "optimi")):
+        sys.path.insert(0, ref_dir)
+        import optimi
+
+    class Block(nn.Module):
+        def __init__(self, d, h, f):
+            super().__init__()
+            self.h = h
+            self.ln1, self.ln2 = nn.LayerNorm(d), nn.LayerNorm(d)
+            self.q, self.k, self.v, self.o = nn.Linear(d, d), nn.Linear(d, d), nn.Linear(d, d), nn.Linear(d, d)
+            self.fc, self.proj = nn.Linear(d, f), nn.Linear(f, d)
+
+        def forward(self, x):
+            B, S, D = x.shape
+            y = self.ln1(x)
+            q, k, v = (m(y).view(B, S, self.h, D // self.h).transpose(1, 2) for m in (self.q, self.k, self.v))
+            x = x + self.o(Fn.scaled_dot_product_attention(q, k, v, is_causal=True).transpose(1, 2).reshape(B, S, D))
+            return x + self.proj(Fn.gelu(self.fc(self.ln2(x))))
+
+    class GPT(nn.Module):
+        def __init__(self, layers=24, d=1024, h=16, f=4096, vocab=50304, ctx=1024):
+            super().__init__()
+            self.wte, self.wpe = nn.Embedding(vocab, d), nn.Embedding(ctx, d)
+            self.blocks = nn.ModuleList([Block(d, h, f) for _ in range(layers)])
+            self.ln_f = nn.LayerNorm(d)
+
+        def forward(self, idx):
+            x = self.wte(idx) + self.wpe(torch.arange(idx.shape[1], device=idx.device))
+            for b in self.blocks:
+                x = b(x)
+            return self.ln_f(x) @ self.wte.weight.t()
+
+    def run(mode):
+        torch.manual_seed(0)
+        model = GPT().to("cuda", torch.bfloat16)
+        params = list(model.parameters())
+        kw = dict(lr=3e-4, weight_decay=1e-2)
+        opt = None
+        if mode.startswith("optimi_b200"):
+            opt = optimi_b200.AdamW(params, gradient_release=True, **kw)
+            if mode.endswith("side_stream"):
+                opt.use_release_stream(True)
+            optimi_b200.prepare_for_gradient_release(model, opt)
+        elif mode.startswith("reference"):
+            opt = optimi.AdamW(params, gradient_release=True, triton=mode.endswith("triton"), foreach=False, **kw)
+            optimi.prepare_for_gradient_release(model, opt)
+        gen = torch.Generator(device="cuda").manual_seed(1)
+
+        def micro(i):
+            if opt is not None:
+                opt.optimizer_accumulation = i % 4 != 3
+            idx = torch.randint(0, 50304, (8, 1024), device="cuda", generator=gen)
+            Fn.cross_entropy(model(idx).float().view(-1, 50304), idx.view(-1)).backward()
+            if opt is None and i % 4 == 3:
+                for p in params:
+                    p.grad = None
+
+        for i in range(8):
+            micro(i)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        launches0 = optimi_b200._lib.LIB.optimi_b200_launch_count()
+        e0.record()
+        for i in range(args.steps):
+            micro(i)
+        e1.record()
+        torch.cuda.synchronize()
+        return {"ms_per_micro_step": e0.elapsed_time(e1) / args.steps, "n_tensors": len(params),
+                "n_params": sum(p.numel() for p in params), "peak_gb": torch.cuda.max_memory_allocated() / 1e9,
+                "gpu_launches": optimi_b200._lib.LIB.optimi_b200_launch_count() - launches0}  # fmt: skip
+
+    modes = ["no_optimizer", "optimi_b200", "optimi_b200_side_stream"] + (["reference_triton", "reference_aten"] if optimi else [])
+    res = {}
+    for m in modes:
+        torch.cuda.reset_peak_memory_stats()
+        res[m] = run(m)
+        import gc
+
+        gc.collect()  # the hooks keep model <-> optimizer cycles alive until collected
+        torch.cuda.empty_cache()
+    base = res["no_optimizer"]["ms_per_micro_step"]
+    line = {
+        "metric": "gradient release + 4-step optimizer accumulation, AdamW bf16+Kahan: device ms per micro-step (fwd+bwd+released steps)",
+        "value": res["optimi_b200"]["ms_per_micro_step"], "unit": "ms", "higher_is_better": False, "n_gpus": 1, "steps": args.steps,
+        "config": {"workload": "24-layer GPT-style decoder, d_model 1024, 16 heads, FFN 4096, vocab 50304, bf16, batch 8 x seq 1024"},
+        "data": "synthetic", "dtype": "bf16", "results": res,
+        "optimizer_overhead_ms": {k: v["ms_per_micro_step"] - base for k, v in res.items() if k != "no_optimizer"},
+    }  # fmt: skip
+    print(json.dumps(line))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="optimi_b200", choices=["optimi_b200", "reference"])
-    ap.add_argument("--workload", default="llama3-8b", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="llama3-8b", choices=sorted(WORKLOADS) + ["gpt-gradient-release"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--exchange", default="auto", choices=["auto", "push", "nccl"], help="N>1: how updated parameters reach the other ranks")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.workload == "gpt-gradient-release":
+        run_gradient_release(args)
+    elif args.impl == "reference":
         run_reference_arm(args)
     else:
         run_b200_arm(args)
