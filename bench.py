@@ -45,6 +45,26 @@ NCU_DRAM_BYTES_PER_PARAM = 17.83
 
 HYPER = dict(lr=3e-4, betas=(0.9, 0.99), weight_decay=1e-5, eps=1e-6, decouple_lr=True)
 
+# --optimizer: class name, constructor keywords (BASELINE configs 3 and 4), algorithmic bytes per parameter in
+# bf16 + Kahan (streams read + written, 2 B each), kernel name for the roofline object
+OPTIMIZERS = {
+    "adamw": ("AdamW", HYPER, 18, "mta_kernel<bf16, AdamOp<kahan,update>>"),
+    "adam": ("Adam", dict(lr=3e-4, betas=(0.9, 0.99), eps=1e-6), 18, "mta_kernel<bf16, AdamOp<kahan,update>>"),
+    "lion": ("Lion", dict(lr=1e-4, betas=(0.9, 0.99)), 14, "mta_kernel<bf16, LionOp<kahan,update>>"),
+    "sgd": ("SGD", dict(lr=1e-2, momentum=0.9), 14, "mta_kernel<bf16, SgdOp<kahan,update>>"),
+    "stableadamw": ("StableAdamW", dict(lr=3e-4), 22, "stable_moments_sum_kernel + mta_kernel<bf16, StableUpdateOp<kahan>>"),
+    "adan": ("Adan", dict(lr=3e-4, betas=(0.98, 0.92, 0.99), kahan_sum=True), 26, "mta_kernel<bf16, AdanOp<kahan,update>>"),
+    "radam": ("RAdam", dict(lr=3e-4), 18, "mta_kernel<bf16, RangerOp<kahan,update>>"),
+    # Lookahead (k=6) reads and writes the slow weights on every 6th step: 18 + 4/6 bytes on average
+    "ranger": ("Ranger", dict(lr=3e-4, k=6, alpha=0.5), 18 + 4 / 6, "mta_kernel<bf16, RangerOp<kahan,update>>"),
+}
+
+
+def metric_name(optimizer: str) -> str:
+    if optimizer == "adamw":
+        return METRIC
+    return f"{OPTIMIZERS[optimizer][0]} bf16-Kahan step: Gparams/s & HBM GB/s vs 8 TB/s, 1/2/4/8 GPU"
+
 
 def llama_shapes(hidden, layers, ffn, q_heads, kv_heads, head_dim, vocab):
     """Parameter shapes of a Llama-style decoder in Hugging Face order (untied output head)."""
@@ -71,16 +91,16 @@ def numel(shape):
     return math.prod(shape)
 
 
-def make_config(workload: str, n_gpus: int, exchange: str = "auto") -> dict:
+def make_config(workload: str, n_gpus: int, exchange: str = "auto", optimizer: str = "adamw") -> dict:
     """The `config` object of the JSON line; identical for both arms of one (workload, N)."""
     shapes = WORKLOADS[workload]()
     n_params = sum(numel(s) for s in shapes)
     return {
-        "workload": f"AdamW bf16+Kahan, decouple_lr, {workload} parameter shapes ({n_params} params, {len(shapes)} tensors)",
-        "optimizer": "AdamW", "lr": HYPER["lr"], "weight_decay": HYPER["weight_decay"], "decouple_lr": True,
+        "workload": f"{OPTIMIZERS[optimizer][0]} bf16+Kahan, {workload} parameter shapes ({n_params} params, {len(shapes)} tensors)",
+        "optimizer": OPTIMIZERS[optimizer][0], "hyper": {k: (list(v) if isinstance(v, tuple) else v) for k, v in OPTIMIZERS[optimizer][1].items()},
         "sharding": "none" if n_gpus == 1 else f"ZeRO-1 over {n_gpus} ranks, exchange={exchange} "
                     "(push: step kernel stores updated params into the peers over NVLink; nccl: all-gather after the step)",
-        "l2": "inputs larger than L2, no flush between steps: %.1f GB streamed per rank per step" % (BYTES_PER_PARAM * n_params / n_gpus / 1e9),
+        "l2": "inputs larger than L2, no flush between steps: %.1f GB streamed per rank per step" % (OPTIMIZERS[optimizer][2] * n_params / n_gpus / 1e9),
     }  # fmt: skip
 
 
@@ -199,7 +219,7 @@ def cpu_sample_shapes(workload):
     return shapes[1:10]
 
 
-def time_cpu_reference(workload, steps, warmup, budget_s=25.0):
+def time_cpu_reference(workload, steps, warmup, budget_s=25.0, optimizer="adamw"):
     """Returns (Gparams/s, kind, cores, sample description).  One step = one optimizer step over the
     sample, AdamW bf16 + Kahan with the benchmark's hyper-parameters, all host threads."""
     shapes = cpu_sample_shapes(workload)
@@ -221,7 +241,7 @@ def time_cpu_reference(workload, steps, warmup, budget_s=25.0):
 
             with warnings.catch_warnings():
                 warnings.simplefilter("ignore")
-                opt = optimi.AdamW(params, foreach=True, triton=False, **HYPER)
+                opt = getattr(optimi, OPTIMIZERS[optimizer][0])(params, foreach=True, triton=False, **OPTIMIZERS[optimizer][1])
             kind = "reference"
 
             def one_step():
@@ -235,7 +255,7 @@ def time_cpu_reference(workload, steps, warmup, budget_s=25.0):
     if kind == "port":
         from oracle.port import OracleOptimizer
 
-        opt = OracleOptimizer("adamw", [p.detach() for p in params], **HYPER)
+        opt = OracleOptimizer(optimizer, [p.detach() for p in params], **OPTIMIZERS[optimizer][1])
 
         def one_step():
             gs = [g.clone() for g in grads]
@@ -259,12 +279,12 @@ def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    value, kind, cores, sample, ms, done = time_cpu_reference(args.workload, args.steps, args.warmup, budget_s=150.0)
+    value, kind, cores, sample, ms, done = time_cpu_reference(args.workload, args.steps, args.warmup, budget_s=150.0, optimizer=args.optimizer)
     line = {
-        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": done,
+        "impl": "reference", "metric": metric_name(args.optimizer), "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": done,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
-        "config": make_config(args.workload, args.gpus, args.exchange),
+        "config": make_config(args.workload, args.gpus, args.exchange, args.optimizer),
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -289,13 +309,15 @@ def run_b200_arm(args):
     shapes = WORKLOADS[args.workload]()
     n_params = sum(numel(s) for s in shapes)
 
+    cls_name, opt_kw, bytes_per_param, kernel_name = OPTIMIZERS[args.optimizer]
+    opt_cls = getattr(optimi_b200, cls_name)
     params = [p.requires_grad_(True) for p in make_params(shapes, device, dtype, seed=0)]
     if world == 1:
-        opt = optimi_b200.AdamW(params, **HYPER)
+        opt = opt_cls(params, **opt_kw)
         step_targets = params
         sharded = None
     else:
-        sharded = ShardedOptimizer(optimi_b200.AdamW, params, exchange=args.exchange, **HYPER)
+        sharded = ShardedOptimizer(opt_cls, params, exchange=args.exchange, **opt_kw)
         opt = sharded
         step_targets = sharded.shard_params
     n_local = sum(t.numel() for t in step_targets)
@@ -393,13 +415,14 @@ def run_b200_arm(args):
     else:
         peak, peak_kind = FALLBACK_HBM_GBS, "fallback"
     kernel_launches_per_step = max(1, launches // args.steps)
-    achieved = BYTES_PER_PARAM * n_local / (step_ms_max * 1e-3) / 1e9
-    traffic = NCU_DRAM_BYTES_PER_PARAM * n_local / kernel_launches_per_step
+    achieved = bytes_per_param * n_local / (step_ms_max * 1e-3) / 1e9
+    traffic = NCU_DRAM_BYTES_PER_PARAM * n_local / kernel_launches_per_step if args.optimizer == "adamw" else None
     roofline = {
         "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": traffic,
         "traffic_note": "bytes per launch: ncu dram read+write of a 336 M-param capture (17.83 B/param) scaled by elements per launch",
-        "peak_kind": f"of {peak_kind}", "frac_of_8TBs": achieved / 8000.0, "kernel": "mta_kernel<bf16, AdamOp<kahan,update>>",
-        "algorithmic_bytes_per_launch": BYTES_PER_PARAM * n_local / kernel_launches_per_step,
+        "peak_kind": f"of {peak_kind}", "frac_of_8TBs": achieved / 8000.0, "kernel": kernel_name,
+        "algorithmic_bytes_per_launch": bytes_per_param * n_local / kernel_launches_per_step,
+        "algorithmic_bytes_per_param": bytes_per_param,
         "launches_per_step": kernel_launches_per_step,
     }  # fmt: skip
 
@@ -412,14 +435,14 @@ def run_b200_arm(args):
 
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
-        v, kind, cores, sample, _, _ = time_cpu_reference(args.workload, 12, 2, budget_s=20.0)
+        v, kind, cores, sample, _, _ = time_cpu_reference(args.workload, 12, 2, budget_s=20.0, optimizer=args.optimizer)
         cpu = {"value": v, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample}
 
     line = {
-        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "metric": metric_name(args.optimizer), "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
-        "config": make_config(args.workload, world, args.exchange),
+        "config": make_config(args.workload, world, args.exchange, args.optimizer),
         "exchange": None if sharded is None else sharded.exchange,
         "hbm_gbs": achieved, "step_ms": step_ms_max, "gather_ms": gather_ms_max, "wall_ms_per_step": t_wall * 1e3 / args.steps,
         "roofline": roofline, "nvlink": nvlink, "cpu_baseline": cpu,
@@ -547,6 +570,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="optimi_b200", choices=["optimi_b200", "reference"])
     ap.add_argument("--workload", default="llama3-8b", choices=sorted(WORKLOADS) + ["gpt-gradient-release"])
+    ap.add_argument("--optimizer", default="adamw", choices=sorted(OPTIMIZERS), help="default: the headline AdamW")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--exchange", default="auto", choices=["auto", "push", "nccl"], help="N>1: how updated parameters reach the other ranks")
     args = ap.parse_args()

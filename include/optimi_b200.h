@@ -63,21 +63,19 @@ int optimi_b200_adam(int n_tensors, void* const* params, void* const* grads, voi
                      double lr, double beta1_comp, double beta2_hat, double beta2_comp, double weight_decay,
                      double eps, int decouple_wd, int kahan_sum, int update_parameters, void* stream);
 
-/* Adam / AdamW step fused with the exchange of a sharded (ZeRO-1) run.  No counterpart in the
- * reference, which has no distributed code: it stands for "optimi_b200_adam on this rank's shard,
- * then all-gather the updated parameters".  Every rank keeps the whole parameter buffer;
- * `peer_deltas[j]` (j < n_peers <= 7) is the byte distance from this rank's copy of that buffer to
- * peer j's copy as mapped into this process (e.g. the buffer pointers of a symmetric-memory
- * allocation), a multiple of 16.  Each updated parameter vector is stored locally and, with plain
- * peer stores over NVLink, at the same offset in every peer's copy, tile by tile as the step
- * proceeds.  The kernel waits for nobody; the caller must order the ranks after the launch (any
- * stream-ordered collective or barrier) before the pushed values are read on the peers.  Always a
- * full update (there is no accumulation-only form: nothing would be pushed). */
-int optimi_b200_adam_push(int n_tensors, void* const* params, void* const* grads, void* const* exp_avgs,
-                          void* const* exp_avg_sqs, void* const* kahan_comps, const int64_t* numels, int dtype,
-                          double lr, double beta1_comp, double beta2_hat, double beta2_comp, double weight_decay,
-                          double eps, int decouple_wd, int kahan_sum, int n_peers, const int64_t* peer_deltas,
-                          void* stream);
+/* Fusing the step with the parameter exchange of a sharded (ZeRO-1) run.  No counterpart in the
+ * reference, which has no distributed code: it stands for "step this rank's shard, then all-gather
+ * the updated parameters".  Every rank keeps the whole parameter buffer; `peer_deltas[j]`
+ * (j < n_peers <= 7) is the byte distance from this rank's copy of that buffer to peer j's copy as
+ * mapped into this process (e.g. the buffer pointers of a symmetric-memory allocation), a multiple
+ * of 16.  Between optimi_b200_push_begin and optimi_b200_push_end every parameter-updating launch
+ * the CALLING THREAD makes through any entry point of this library stores each updated parameter
+ * vector locally and, with plain peer stores over NVLink, at the same offset in every peer's copy,
+ * tile by tile as the step proceeds.  The kernels wait for nobody; the caller must order the ranks
+ * after the launches (any stream-ordered collective or barrier) before the pushed values are read
+ * on the peers.  Accumulation-only steps (update_parameters == 0) push nothing. */
+int optimi_b200_push_begin(int n_peers, const int64_t* peer_deltas);
+void optimi_b200_push_end(void);
 
 /* Lion.  Replaces _foreach_lion (optimi/lion.py:341-380), _single_param_lion (optimi/lion.py:301-338)
  * and the Triton launchers (optimi/lion.py:453-530).  `weight_decay` is the folded factor

@@ -27,7 +27,6 @@ _I = ctypes.c_int
 # name -> argument types after (n_tensors) and the pointer lists; mirrors include/optimi_b200.h
 SIGNATURES = {
     "optimi_b200_adam": [_I] + [_P] * 5 + [_P, _I] + [_D] * 6 + [_I] * 3 + [_P],
-    "optimi_b200_adam_push": [_I] + [_P] * 5 + [_P, _I] + [_D] * 6 + [_I] * 2 + [_I, _P, _P],
     "optimi_b200_lion": [_I] + [_P] * 4 + [_P, _I] + [_D] * 4 + [_I] * 2 + [_P],
     "optimi_b200_sgd": [_I] + [_P] * 4 + [_P, _I] + [_D] * 3 + [_I] * 4 + [_P],
     "optimi_b200_stableadamw": [_I] + [_P] * 5 + [_P, _I] + [_D] * 6 + [_I, _D, _I, _I, _P, ctypes.c_size_t, _P],
@@ -36,7 +35,7 @@ SIGNATURES = {
     "optimi_b200_radam": [_I] + [_P] * 5 + [_P, _I] + [_D] * 6 + [_I, _D] + [_I] * 3 + [_P],
     "optimi_b200_ranger": [_I] + [_P] * 6 + [_P, _I] + [_D] * 6 + [_I, _D, _I, _D] + [_I] * 3 + [_P],
 }
-EXPORTS = list(SIGNATURES) + ["optimi_b200_last_error", "optimi_b200_version", "optimi_b200_launch_count", "optimi_b200_stableadamw_workspace_bytes"]
+EXPORTS = list(SIGNATURES) + ["optimi_b200_push_begin", "optimi_b200_push_end", "optimi_b200_last_error", "optimi_b200_version", "optimi_b200_launch_count", "optimi_b200_stableadamw_workspace_bytes"]
 
 
 def _load() -> ctypes.CDLL:
@@ -52,6 +51,10 @@ def _load() -> ctypes.CDLL:
     lib.optimi_b200_last_error.restype = ctypes.c_char_p
     lib.optimi_b200_last_error.argtypes = []
     lib.optimi_b200_version.restype = _I
+    lib.optimi_b200_push_begin.restype = _I
+    lib.optimi_b200_push_begin.argtypes = [_I, _P]
+    lib.optimi_b200_push_end.restype = None
+    lib.optimi_b200_push_end.argtypes = []
     lib.optimi_b200_launch_count.restype = ctypes.c_ulonglong
     lib.optimi_b200_launch_count.argtypes = []
     lib.optimi_b200_stableadamw_workspace_bytes.restype = ctypes.c_size_t
@@ -61,6 +64,21 @@ def _load() -> ctypes.CDLL:
 
 LIB = _load()
 LIB_PATH = _OVERRIDE or _build.LIB
+
+
+class peer_push:
+    """Context manager: launches made by this thread inside it also store updated parameters into the
+    peers' copies of the parameter buffer (`deltas`: byte offsets to those copies)."""
+
+    def __init__(self, deltas):
+        self.deltas = (ctypes.c_int64 * len(deltas))(*deltas)
+
+    def __enter__(self):
+        check(LIB.optimi_b200_push_begin(len(self.deltas), ctypes.cast(self.deltas, ctypes.c_void_p)))
+        return self
+
+    def __exit__(self, *exc):
+        LIB.optimi_b200_push_end()
 
 
 def check(rc: int) -> None:

@@ -128,6 +128,22 @@ static int launch_op(const char* name, int n, const int64_t* numels, void* const
   });
 }
 
+// Peer push requested for the calling thread's next launches (optimi_b200_push_begin / _end).
+static thread_local PeerPush g_push = {0, {0}};
+
+// Launches Op, or PushOp<Op> when a peer push is active.
+template <typename T, class Op>
+static int launch_maybe_push(const char* name, int n, const int64_t* numels, void* const* const (&lists)[Op::NL],
+                             const typename Op::Args& args, cudaStream_t stream) {
+  if (g_push.n > 0) {
+    PushArgs<typename Op::Args> pa;
+    pa.base = args;
+    pa.push = g_push;
+    return launch_op<T, PushOp<Op>>(name, n, numels, lists, pa, stream);
+  }
+  return launch_op<T, Op>(name, n, numels, lists, args, stream);
+}
+
 // Picks the instantiation for (dtype, kahan, update).  Kahan compensation exists only for the
 // 16-bit storage types, as in the reference (e.g. optimi/adam.py:421).
 template <template <bool, bool> class Op, class Lists, class Args>
@@ -136,13 +152,13 @@ static int dispatch(const char* name, int dtype, bool kahan, bool update, int n,
 #define OPTIMI_GO(T)                                                                                   \
   do {                                                                                                 \
     if (!update) return launch_op<T, Op<false, false>>(name, n, numels, lists, args, stream);          \
-    if (kahan) return launch_op<T, Op<true, true>>(name, n, numels, lists, args, stream);              \
-    return launch_op<T, Op<false, true>>(name, n, numels, lists, args, stream);                        \
+    if (kahan) return launch_maybe_push<T, Op<true, true>>(name, n, numels, lists, args, stream);      \
+    return launch_maybe_push<T, Op<false, true>>(name, n, numels, lists, args, stream);                \
   } while (0)
   switch (dtype) {
     case OPTIMI_F32:
       if (!update) return launch_op<float, Op<false, false>>(name, n, numels, lists, args, stream);
-      return launch_op<float, Op<false, true>>(name, n, numels, lists, args, stream);
+      return launch_maybe_push<float, Op<false, true>>(name, n, numels, lists, args, stream);
     case OPTIMI_BF16: OPTIMI_GO(__nv_bfloat16);
     case OPTIMI_F16: OPTIMI_GO(__half);
   }
@@ -278,9 +294,9 @@ static int stableadamw_typed(int n, void* const* params, void* const* grads, voi
   ua.has_wd = weight_decay != 0;
   void* const* const lists_b[4] = {params, exp_avgs, exp_avg_sqs, kahan ? kahan_comps : nullptr};
   if constexpr (sizeof(T) == 2) {  // Kahan compensation exists for the 16-bit storage types only
-    if (kahan) return launch_op<T, StableUpdateOp<true>>("optimi_b200_stableadamw (update)", n, numels, lists_b, ua, stream);
+    if (kahan) return launch_maybe_push<T, StableUpdateOp<true>>("optimi_b200_stableadamw (update)", n, numels, lists_b, ua, stream);
   }
-  return launch_op<T, StableUpdateOp<false>>("optimi_b200_stableadamw (update)", n, numels, lists_b, ua, stream);
+  return launch_maybe_push<T, StableUpdateOp<false>>("optimi_b200_stableadamw (update)", n, numels, lists_b, ua, stream);
 }
 
 static int wd_mode_of(double weight_decay, int decouple_wd) {
@@ -299,6 +315,19 @@ extern "C" {
 const char* optimi_b200_last_error(void) { return g_error; }
 
 int optimi_b200_version(void) { return 100; }
+
+int optimi_b200_push_begin(int n_peers, const int64_t* peer_deltas) {
+  const char* fn = "optimi_b200_push_begin";
+  if (n_peers < 0 || n_peers > kMaxPeers) return fail(OPTIMI_ERR_INVALID_ARGUMENT, "%s: n_peers=%d is outside 0..%d", fn, n_peers, kMaxPeers);
+  if (n_peers > 0 && !peer_deltas) return fail(OPTIMI_ERR_INVALID_ARGUMENT, "%s: peer_deltas is NULL", fn);
+  for (int j = 0; j < n_peers; j++)
+    if (peer_deltas[j] % 16) return fail(OPTIMI_ERR_INVALID_ARGUMENT, "%s: peer_deltas[%d] is not a multiple of 16 bytes", fn, j);
+  g_push.n = n_peers;
+  for (int j = 0; j < kMaxPeers; j++) g_push.delta[j] = j < n_peers ? (long long)peer_deltas[j] : 0;
+  return OPTIMI_OK;
+}
+
+void optimi_b200_push_end(void) { g_push.n = 0; }
 
 unsigned long long optimi_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
@@ -322,34 +351,6 @@ int optimi_b200_adam(int n, void* const* params, void* const* grads, void* const
   a.neg_lr = (float)(-lr);
   a.wd_mode = wd_mode_of(weight_decay, decouple_wd);
   return dispatch<AdamOp>("optimi_b200_adam", dtype, kahan, update, n, numels, lists, a, (cudaStream_t)stream);
-}
-
-int optimi_b200_adam_push(int n, void* const* params, void* const* grads, void* const* exp_avgs, void* const* exp_avg_sqs,
-                          void* const* kahan_comps, const int64_t* numels, int dtype, double lr, double beta1_comp,
-                          double beta2_hat, double beta2_comp, double weight_decay, double eps, int decouple_wd, int kahan_sum,
-                          int n_peers, const int64_t* peer_deltas, void* stream) {
-  const char* fn = "optimi_b200_adam_push";
-  if (n_peers < 0 || n_peers > kMaxPeers) return fail(OPTIMI_ERR_INVALID_ARGUMENT, "%s: n_peers=%d is outside 0..%d", fn, n_peers, kMaxPeers);
-  if (n_peers > 0 && !peer_deltas) return fail(OPTIMI_ERR_INVALID_ARGUMENT, "%s: peer_deltas is NULL", fn);
-  const bool kahan = kahan_sum && kahan_comps && low_precision(dtype);
-  void* const* const lists[5] = {params, grads, exp_avgs, exp_avg_sqs, kahan ? kahan_comps : nullptr};
-  const bool req[5] = {true, true, true, true, kahan};
-  static const char* const names[5] = {"params", "grads", "exp_avgs", "exp_avg_sqs", "kahan_comps"};
-  int rc = check_lists(fn, n, numels, dtype, 5, lists, req, names);
-  if (rc != OPTIMI_OK || n == 0) return rc;
-  PushArgs<AdamArgs> a;
-  a.base.l1 = make_lerp(beta1_comp);
-  a.base.beta2_hat = (float)beta2_hat;
-  a.base.beta2_comp = (float)beta2_comp;
-  a.base.wd = (float)weight_decay;
-  a.base.eps = (float)eps;
-  a.base.neg_lr = (float)(-lr);
-  a.base.wd_mode = wd_mode_of(weight_decay, decouple_wd);
-  a.push.n = n_peers;
-  for (int j = 0; j < kMaxPeers; j++) a.push.delta[j] = j < n_peers ? (long long)peer_deltas[j] : 0;
-  for (int j = 0; j < n_peers; j++)
-    if (peer_deltas[j] % 16) return fail(OPTIMI_ERR_INVALID_ARGUMENT, "%s: peer_deltas[%d] is not a multiple of 16 bytes", fn, j);
-  return dispatch<AdamPushOp>(fn, dtype, kahan, true, n, numels, lists, a, (cudaStream_t)stream);
 }
 
 int optimi_b200_radam(int n, void* const* params, void* const* grads, void* const* exp_avgs, void* const* exp_avg_sqs,

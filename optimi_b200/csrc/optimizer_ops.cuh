@@ -126,9 +126,6 @@ struct PushOp {
   static __device__ __forceinline__ void elem(float (&e)[NL], const Args& a, const Ctx& ctx) { Base::template elem<T>(e, a.base, ctx); }
 };
 
-template <bool KAHAN, bool UPDATE>
-using AdamPushOp = PushOp<AdamOp<KAHAN, UPDATE>>;
-
 // ---------------------------------------------------------------------------------------------
 // RAdam and Ranger              lists: 0 p, 1 g, 2 m, 3 v, 4 k, 5 la (slow weights, Ranger only)
 // optimi/radam.py:438-479, optimi/ranger.py:498-561

@@ -54,25 +54,13 @@ def adam(
     optimizer_accumulation: bool = False,
     _stream=None,
     _trusted: bool = False,
-    _push=None,
 ):
-    """Adam / AdamW step on lists of tensors (or bare tensors in gradient-release form).
-
-    `_push` (a sequence of byte offsets to the peers' copies of the parameter buffer) selects the
-    fused step + exchange kernel of a sharded run; see `optimi_b200.zero.ShardedOptimizer`.
-    """
+    """Adam / AdamW step on lists of tensors (or bare tensors in gradient-release form)."""
     t = _advance(step)
     tail = T.adam_tail(t, not optimizer_accumulation, lr=lr, beta1=beta1, beta2=beta2, weight_decay=weight_decay, eps=eps,
                        decouple_wd=decouple_wd, decouple_lr=decouple_lr, max_lr=max_lr, kahan_sum=kahan_sum)  # fmt: skip
     lists = [params, grads, exp_avgs, exp_avg_sqs, kahan_comps]
     names = ("params", "grads", "exp_avgs", "exp_avg_sqs", "kahan_comps")
-    if _push is not None and not optimizer_accumulation:
-        import ctypes
-
-        deltas = (ctypes.c_int64 * len(_push))(*_push)
-        push_tail = tail[:-1] + (len(_push), ctypes.cast(deltas, ctypes.c_void_p))
-        launch("optimi_b200_adam_push", lists, names, lambda *_: push_tail, _stream, _trusted)
-        return
     launch("optimi_b200_adam", lists, names, lambda *_: tail, _stream, _trusted)
 
 
@@ -98,13 +86,12 @@ def adamw(
     optimizer_accumulation: bool = False,
     _stream=None,
     _trusted: bool = False,
-    _push=None,
 ):
     """AdamW step: `adam` with decoupled weight decay (optimi/adamw.py:123-143)."""
     adam(
         params, grads, exp_avgs, exp_avg_sqs, kahan_comps, lr=lr, beta1=beta1, beta2=beta2, weight_decay=weight_decay,
         eps=eps, step=step, decouple_wd=True, decouple_lr=decouple_lr, max_lr=max_lr, kahan_sum=kahan_sum,
-        gradient_release=gradient_release, optimizer_accumulation=optimizer_accumulation, _stream=_stream, _trusted=_trusted, _push=_push,
+        gradient_release=gradient_release, optimizer_accumulation=optimizer_accumulation, _stream=_stream, _trusted=_trusted,
     )  # fmt: skip
 
 

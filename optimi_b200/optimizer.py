@@ -75,7 +75,6 @@ class OptimiOptimizer(Optimizer):
     _list_args: tuple[str, ...] = ()  # functional list arguments after params, grads, in order; names of state keys
     _state_arg_names: dict[str, str] = {}  # state key -> functional keyword
     _counts_steps = True  # keeps a `step` counter (Lion and SGD do not)
-    _supports_push = False  # has a fused step + peer-push kernel (sharded runs)
     _c_fn: str = ""  # C entry point
     _c_states: tuple[str, ...] = ()  # state keys in the order of the C signature (after params, grads)
     _tail: Callable = None  # host scalars -> C arguments (optimi_b200._tails)
@@ -115,7 +114,6 @@ class OptimiOptimizer(Optimizer):
                 )
 
         self._optimizer_accumulation = False
-        self._peer_push: list[int] | None = None  # set by zero.ShardedOptimizer: byte offsets to the peers' parameter buffers
         self._plans: dict[Tensor, _ReleasePlan] = {}  # gradient release: cached C arguments per parameter
         self._tail_cache: dict[int, tuple] = {}  # id(group) -> (key, tail): scalars are shared by a group's parameters
         self._release_stream: torch.cuda.Stream | None = None
@@ -205,8 +203,6 @@ class OptimiOptimizer(Optimizer):
                 kw = self._keywords(group)
                 if self._counts_steps:
                     kw["step"] = group["step"]
-                if self._peer_push is not None and self._supports_push:
-                    kw["_push"] = self._peer_push
                 if not params:
                     if self._counts_steps:
                         group["step"].add_(1)  # the reference advances the counter before looking at the lists
@@ -344,7 +340,6 @@ class Adam(OptimiOptimizer):
 
     _functional = staticmethod(F.adam)
     _c_fn, _c_states, _tail = "optimi_b200_adam", ("exp_avg", "exp_avg_sq", "kahan_comp"), staticmethod(T.adam_tail)
-    _supports_push = True
     _list_args = ("exp_avg", "exp_avg_sq", "kahan_comp")
     _state_arg_names = {"exp_avg": "exp_avgs", "exp_avg_sq": "exp_avg_sqs", "kahan_comp": "kahan_comps"}
     _scalar_keys = ("lr", "beta1", "beta2", "weight_decay", "eps", "decouple_wd", "decouple_lr", "max_lr")
@@ -407,7 +402,6 @@ class RAdam(Adam):
 
     _functional = staticmethod(F.radam)
     _c_fn, _tail = "optimi_b200_radam", staticmethod(T.radam_tail)
-    _supports_push = False
 
 
 class Ranger(OptimiOptimizer):

@@ -15,10 +15,10 @@ Exchange modes (`exchange=`):
     "nccl"   step the local range, then all-gather (works everywhere, any optimizer).
     "push"   the flat buffers are symmetric-memory allocations mapped into every rank; the step kernel
              itself stores each updated parameter vector into every peer's buffer over NVLink as it
-             goes (`optimi_b200_adam_push`), so the exchange overlaps the step tile by tile.  The
-             ranks then meet in a one-element all-reduce on the same stream, which orders every
-             rank's later work after all pushes.  Available for Adam/AdamW on CUDA; other optimizers
-             and CPU groups fall back to "nccl".
+             goes (`optimi_b200_push_begin` around the step), so the exchange overlaps the step tile
+             by tile.  The ranks then meet in a one-element all-reduce on the same stream, which
+             orders every rank's later work after all pushes.  Needs an optimi_b200 optimizer on 2-8
+             CUDA ranks and one parameter dtype; anything else falls back to "nccl".
     "auto"   "push" when available, else "nccl".
 
 Sharded and unsharded runs produce bit-identical parameters: each element sees exactly the same
@@ -102,11 +102,11 @@ class ShardedOptimizer:
             split_on_tensors = getattr(optimizer_cls, "__name__", "") == "StableAdamW"
         self.gather = gather
         can_push = (
-            self.world > 1 and self.world <= 8 and getattr(optimizer_cls, "_supports_push", False) and not split_on_tensors
+            self.world > 1 and self.world <= 8 and hasattr(optimizer_cls, "_c_fn")
             and all(p.is_cuda for p in self.params) and len({(p.device, p.dtype) for p in self.params}) == 1
         )  # fmt: skip
         if exchange == "push" and not can_push:
-            raise ValueError("exchange='push' needs 2-8 CUDA ranks, one dtype, and an optimizer with a push kernel (Adam, AdamW)")
+            raise ValueError("exchange='push' needs 2-8 CUDA ranks, one parameter dtype and an optimi_b200 optimizer")
         self.exchange = "push" if (exchange in ("push", "auto") and can_push) else "nccl"
         self._peer_deltas: list[int] | None = None
         self._symm_handles = []
@@ -137,7 +137,6 @@ class ShardedOptimizer:
         self.shard_params = shard_params
         self.inner = optimizer_cls(shard_params, **kwargs)
         if self.exchange == "push":
-            self.inner._peer_push = self._peer_deltas
             self._meet = torch.zeros(1, dtype=torch.int32, device=self.params[0].device)
             # no rank may start pushing before every rank has finished filling its own buffer
             torch.cuda.synchronize(self.params[0].device)
@@ -195,7 +194,13 @@ class ShardedOptimizer:
         else:
             for sp, g in zip(self.shard_params, shard_grads):
                 sp.grad = g
-        self.inner.step()
+        if self.exchange == "push":
+            from ._lib import peer_push
+
+            with peer_push(self._peer_deltas):
+                self.inner.step()
+        else:
+            self.inner.step()
 
     @torch.no_grad()
     def gather_params(self):

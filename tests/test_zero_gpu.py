@@ -58,7 +58,12 @@ def _worker(rank, world, port, cname, kw, exchange, out):
     ("AdamW", dict(lr=3e-4, weight_decay=1e-5, decouple_lr=True), "push"),
     ("Adam", dict(lr=3e-4, weight_decay=1e-2, kahan_sum=False), "push"),
     ("StableAdamW", dict(lr=3e-4), "nccl"),
+    ("StableAdamW", dict(lr=3e-4), "push"),
     ("Adan", dict(lr=3e-4, kahan_sum=True), "nccl"),
+    ("Adan", dict(lr=3e-4, kahan_sum=True), "push"),
+    ("Lion", dict(lr=1e-4, weight_decay=0.1), "push"),
+    ("SGD", dict(lr=1e-2, momentum=0.9), "push"),
+    ("Ranger", dict(lr=3e-4, k=2), "push"),
 ])  # fmt: skip
 def test_sharded_step_equals_unsharded(cname, kw, exchange):
     if torch.cuda.device_count() < 2:
