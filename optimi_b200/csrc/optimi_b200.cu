@@ -388,7 +388,8 @@ int optimi_b200_ranger(int n, void* const* params, void* const* grads, void* con
   a.wd_mode = wd_mode_of(weight_decay, decouple_wd);
   a.use_rect = use_rect != 0;
   a.lookahead = look;
-  return dispatch<RangerOp>(fn, dtype, kahan, update, n, numels, lists, a, (cudaStream_t)stream);
+  if (look) return dispatch<RangerLookOp>(fn, dtype, kahan, update, n, numels, lists, a, (cudaStream_t)stream);
+  return dispatch<RadamOp>(fn, dtype, kahan, update, n, numels, lists, a, (cudaStream_t)stream);
 }
 
 int optimi_b200_lion(int n, void* const* params, void* const* grads, void* const* exp_avgs, void* const* kahan_comps,

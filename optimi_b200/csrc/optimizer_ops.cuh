@@ -65,7 +65,10 @@ __device__ __forceinline__ void weight_decay(float& p, float& g, int mode, float
 struct OpBase {
   using Ctx = NoCtx;
   static constexpr int kSumSlot = -1;
-  static constexpr int kMinBlocks = 10;  // <= 51 registers per thread at 128 threads
+#ifndef OPTIMI_MIN_BLOCKS
+#define OPTIMI_MIN_BLOCKS 10
+#endif
+  static constexpr int kMinBlocks = OPTIMI_MIN_BLOCKS;  // 10: <= 51 registers per thread at 128 threads
   static constexpr bool kPush = false;
   template <class Table, class Args>
   static __device__ __forceinline__ NoCtx context(const Table&, const Span&, const Args&) { return NoCtx{}; }
@@ -137,13 +140,15 @@ struct RangerArgs {
   int wd_mode, use_rect, lookahead;
 };
 
-template <bool KAHAN, bool UPDATE>
+// LOOK = true only for the launches of a Ranger step that falls on a lookahead step; RAdam and the
+// other Ranger steps never touch the slow weights and keep Adam's register budget.
+template <bool KAHAN, bool UPDATE, bool LOOK>
 struct RangerOp : OpBase {
   static constexpr int NL = 6, U = OPTIMI_U_ADAM;
-  static constexpr int kMinBlocks = 8;  // six streams: <= 64 registers
+  static constexpr int kMinBlocks = LOOK ? 8 : OPTIMI_MIN_BLOCKS;  // six streams: <= 64 registers; five: as Adam
   using Args = RangerArgs;
-  static __device__ __forceinline__ bool reads(int l, const Args& a) {
-    return l == 0 ? UPDATE : l == 4 ? KAHAN : l == 5 ? (UPDATE && a.lookahead) : true;
+  static __device__ __forceinline__ bool reads(int l, const Args&) {
+    return l == 0 ? UPDATE : l == 4 ? KAHAN : l == 5 ? (UPDATE && LOOK) : true;
   }
   static __device__ __forceinline__ bool writes(int l, const Args& a) { return l != 1 && reads(l, a); }
   template <typename T>
@@ -158,7 +163,7 @@ struct RangerOp : OpBase {
       if (KAHAN) {
         k = x;
         kahan_tail<T>(p, k);
-        if (a.lookahead) {  // optimi/ranger.py:537-549
+        if (LOOK) {  // optimi/ranger.py:537-549
           const float diff = rnd<T>(__fsub_rn(p, la));
           k = rnd<T>(__fmaf_rn(a.alpha, diff, k));
           kahan_tail<T>(la, k);
@@ -166,7 +171,7 @@ struct RangerOp : OpBase {
         }
       } else {
         p = x;
-        if (a.lookahead) {  // optimi/ranger.py:559-561
+        if (LOOK) {  // optimi/ranger.py:559-561
           p = rnd<T>(__fsub_rn(p, la));
           la = rnd<T>(__fmaf_rn(a.alpha, p, la));
           p = la;
@@ -175,6 +180,9 @@ struct RangerOp : OpBase {
     }
   }
 };
+
+template <bool KAHAN, bool UPDATE> using RadamOp = RangerOp<KAHAN, UPDATE, false>;
+template <bool KAHAN, bool UPDATE> using RangerLookOp = RangerOp<KAHAN, UPDATE, true>;
 
 // ---------------------------------------------------------------------------------------------
 // Lion                                                        lists: 0 p, 1 g, 2 m, 3 k
@@ -199,7 +207,7 @@ struct LionOp : OpBase {
     if (UPDATE) {
       if (a.wd_mode == kWdDecoupled) p = rnd<T>(__fmul_rn(p, a.wd));
       u = rnd<T>(lerp_op(m, g, a.l1));
-      u = (float)((0.f < u) - (u < 0.f));
+      u = u > 0.f ? 1.f : (u < 0.f ? -1.f : 0.f);  // sign; NaN -> 0 like (0 < u) - (u < 0)
     }
     m = rnd<T>(lerp_op(m, g, a.l2));
     if (UPDATE) {
