@@ -332,7 +332,11 @@ struct StableMomentsOp : OpBase {
     if (REDUCE) {
       const float x = rnd<T>(fmaxf(v, a.eps_sq));
       const float gg = rnd<T>(__fmul_rn(g, g));
-      e[3] = rnd<T>(__fdiv_rn(gg, x));
+      // full-range approximate division (2 ulp): these terms only feed the per-tensor mean, whose
+      // summation order already differs from the reference's, and this pass is issue-bound
+      float q;
+      asm("div.full.f32 %0, %1, %2;" : "=f"(q) : "f"(gg), "f"(x));
+      e[3] = rnd<T>(q);
     }
   }
 };
