@@ -245,6 +245,91 @@ class ShardedOptimizer:
             sp.grad = None
 
     # checkpoints -------------------------------------------------------------------------------
+    def _exchange(self, flat: Tensor, layout: FlatLayout) -> None:
+        """Every rank ends up with all ranks' ranges of `flat` (each rank has filled its own)."""
+        if self.world == 1:
+            return
+        lo, hi = layout.rank_range(self.rank)
+        sizes = {layout.bounds[r + 1] - layout.bounds[r] for r in range(self.world)}
+        if len(sizes) == 1:
+            dist.all_gather_into_tensor(flat, flat[lo:hi].clone(), group=self.group)
+        else:
+            for r in range(self.world):
+                piece = flat[layout.bounds[r] : layout.bounds[r + 1]]
+                if piece.numel():
+                    src = dist.get_global_rank(self.group, r) if self.group is not None else r
+                    dist.broadcast(piece, src=src, group=self.group)
+
+    def consolidated_state_dict(self) -> dict[str, Any]:
+        """The optimizer state in the UNSHARDED layout of the wrapped optimizer class — what
+        `optimizer_cls(params).state_dict()` would hold after the same steps — on every rank.  Per-element
+        state tensors are put back together from the ranks' ranges; everything else (step counters,
+        0-dim tensors, None) is taken from the rank that owns the tensor's first element.  A collective:
+        all ranks must call it.  The result loads into a plain optimizer of the reference or of this
+        package, or into a `ShardedOptimizer` of any world size (`load_consolidated_state_dict`)."""
+        index_of = {id(p): i for i, p in enumerate(self.params)}
+        state: dict[int, dict[str, Any]] = {}
+        for b in self.buckets:
+            layout, plist = b["layout"], b["params"]
+            device, dtype = b["flat"].device, b["flat"].dtype
+            local = {}
+            for (i, a, e), sp in zip(b["pieces"], b["shards"]):
+                local[(i, a, e)] = self.inner.state.get(sp, {})
+            elem_keys, other = set(), {}
+            for (i, a, e), st in local.items():
+                for k, v in st.items():
+                    if torch.is_tensor(v) and v.dim() > 0 and v.numel() == e - a:
+                        elem_keys.add(k)
+                    elif a == 0:
+                        other.setdefault(i, {})[k] = v.cpu() if torch.is_tensor(v) else v
+            if self.world > 1:
+                gathered = [None] * self.world
+                dist.all_gather_object(gathered, (sorted(elem_keys), other), group=self.group)
+                elem_keys = set().union(*[set(g[0]) for g in gathered])
+                other = {i: kv for g in gathered for i, kv in g[1].items()}
+            for i, p in enumerate(plist):
+                state[index_of[id(p)]] = dict(other.get(i, {}))
+            for k in sorted(elem_keys):
+                flat = torch.zeros(layout.total, dtype=dtype, device=device)
+                for (i, a, e), st in local.items():
+                    if st.get(k) is not None:
+                        flat[layout.offsets[i] + a : layout.offsets[i] + e] = st[k].reshape(-1)
+                self._exchange(flat, layout)
+                for i, p in enumerate(plist):
+                    off = layout.offsets[i]
+                    state[index_of[id(p)]][k] = flat[off : off + p.numel()].view(p.shape).clone()
+                del flat
+        groups = []
+        for g in self.inner.param_groups:
+            groups.append({k: v for k, v in g.items() if k != "params"} | {"params": list(range(len(self.params)))})
+        # parameters that never received a gradient have no state, as in an unsharded optimizer
+        state = {i: st for i, st in state.items() if st}
+        return {"state": state, "param_groups": groups}
+
+    def load_consolidated_state_dict(self, sd: dict[str, Any]) -> None:
+        """Loads an unsharded state dict (from `consolidated_state_dict`, from a plain optimizer of this
+        package or from the reference): every rank keeps the slices of its own range."""
+        inner_sd = self.inner.state_dict()
+        order = [sp for b in self.buckets for sp in b["shards"]]
+        piece_of = [(b, piece) for b in self.buckets for piece in b["pieces"]]
+        index_of = {id(p): i for i, p in enumerate(self.params)}
+        new_state = {}
+        for j, (sp, (b, (i, a, e))) in enumerate(zip(order, piece_of)):
+            full = sd["state"].get(index_of[id(b["params"][i])])
+            if full is None:
+                continue
+            entry = {}
+            for k, v in full.items():
+                if torch.is_tensor(v) and v.dim() > 0 and v.numel() == b["params"][i].numel():
+                    entry[k] = v.reshape(-1)[a:e].clone()
+                else:
+                    entry[k] = v.clone() if torch.is_tensor(v) else v
+            new_state[j] = entry
+        groups = []
+        for g_new, g_old in zip(sd["param_groups"], inner_sd["param_groups"]):
+            groups.append({k: v for k, v in g_new.items() if k != "params"} | {"params": g_old["params"]})
+        self.inner.load_state_dict({"state": new_state, "param_groups": groups})
+
     def state_dict(self) -> dict[str, Any]:
         """This rank's shard of the optimizer state plus the layout needed to put shards back together."""
         return {

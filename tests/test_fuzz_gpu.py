@@ -1,0 +1,106 @@
+"""Randomised parity: seeded random optimizer / hyper-parameter / dtype / shape combinations, kernels
+against the CPU oracle, bit for bit (StableAdamW at its stated tolerance).  Covers corners the fixed
+golden cases do not: betas near 0 and 1, lerp weights on both sides of 0.5, tiny and huge eps, zero
+gradients, zero-size tensors, learning-rate changes between steps, several parameter groups."""
+
+import random
+import warnings
+
+import pytest
+import torch
+
+from helpers import TORCH_DTYPE, ulp_diff, within_ulps_of_scale
+
+pytestmark = pytest.mark.gpu
+
+NAMES = {"adam": "Adam", "adamw": "AdamW", "lion": "Lion", "sgd": "SGD", "stableadamw": "StableAdamW", "adan": "Adan",
+         "radam": "RAdam", "ranger": "Ranger"}  # fmt: skip
+
+
+def random_config(rng: random.Random):
+    opt = rng.choice(list(NAMES))
+    dt = rng.choice(["f32", "bf16", "bf16", "f16"])
+    kw = dict(lr=10 ** rng.uniform(-5, -1.5))
+    beta = lambda: rng.choice([0.0, 0.3, 0.5, 0.6, 0.9, 0.95, 0.99, 0.999])  # noqa: E731
+    if opt in ("adam", "adamw", "radam", "ranger", "stableadamw", "lion"):
+        kw["betas"] = (beta(), beta())
+    if opt == "adan":
+        kw["betas"] = (beta(), beta(), beta())
+    if opt != "lion" and opt != "sgd":
+        kw["eps"] = rng.choice([1e-6, 1e-8, 1e-3, 1e-10])
+    kw["weight_decay"] = rng.choice([0.0, 1e-2, 1e-5, 0.1])
+    if opt in ("adam", "radam", "ranger", "sgd"):
+        kw["decouple_wd"] = rng.random() < 0.5
+    if rng.random() < 0.3:
+        kw["decouple_lr"] = True
+        kw["max_lr"] = kw["lr"] * rng.choice([1.0, 2.0, 10.0])
+        kw["weight_decay"] = min(kw["weight_decay"], 1e-5)
+    if opt == "sgd":
+        kw["momentum"] = rng.choice([0.0, 0.5, 0.9])
+        kw["dampening"] = rng.random() < 0.4
+        kw["torch_init"] = rng.random() < 0.3
+    if opt == "ranger":
+        kw["k"] = rng.choice([1, 2, 3, 6])
+        kw["alpha"] = rng.choice([0.2, 0.5, 0.8])
+    if opt == "adan":
+        kw["kahan_sum"] = dt != "f32" and rng.random() < 0.6
+    elif rng.random() < 0.25:
+        kw["kahan_sum"] = False
+    return opt, dt, kw
+
+
+@pytest.mark.parametrize("seed", range(48))
+def test_random_configuration_matches_oracle(seed):
+    import optimi_b200
+    from cases import STATE_NAMES
+    from oracle.port import OracleOptimizer
+
+    rng = random.Random(1000 + seed)
+    opt, dt, kw = random_config(rng)
+    dtype = TORCH_DTYPE[dt]
+    g = torch.Generator().manual_seed(seed)
+    shapes = [rng.choice([(0,), (1,), (7,), (1000,), (1024,), (129, 65), (4097,), (40_000,)]) for _ in range(rng.randint(1, 6))]
+    host = [(torch.randn(s, generator=g) * rng.choice([0.02, 1.0])).to(dtype) for s in shapes]
+    steps = rng.randint(2, 9)
+    scale = 10 ** rng.uniform(-5, -1)
+    grads = [[(torch.zeros(s) if rng.random() < 0.1 else torch.randn(s, generator=g) * scale).to(dtype) for s in shapes] for _ in range(steps)]
+    lr_schedule = [kw["lr"] * rng.choice([1.0, 0.5, 0.1]) if not kw.get("decouple_lr") else kw["lr"] for _ in range(steps)]
+
+    params = [h.clone().cuda().requires_grad_(True) for h in host]
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        gpu = getattr(optimi_b200, NAMES[opt])(params, **kw)
+    oracle = OracleOptimizer(opt, [h.clone() for h in host], **kw)
+    for it in range(steps):
+        gpu.param_groups[0]["lr"] = lr_schedule[it]
+        oracle.h["lr"] = lr_schedule[it]
+        for p, gr in zip(params, grads[it]):
+            p.grad = gr.cuda()
+        gpu.step()
+        gpu.zero_grad()
+        oracle.step([gr.clone() for gr in grads[it]])
+    torch.cuda.synchronize()
+    for i, p in enumerate(params):
+        if p.numel() == 0:
+            continue
+        pairs = [("param", p.detach().cpu(), oracle.params[i])]
+        for name in STATE_NAMES[opt]:
+            t = gpu.state[p].get(name)
+            if t is not None and t.numel() == p.numel():
+                pairs.append((name, t.cpu(), oracle.state[i][name]))
+        for name, a, b in pairs:
+            where = f"seed {seed} {opt} {dt} {kw} tensor {i} {tuple(p.shape)} {name}"
+            if opt == "stableadamw":
+                if dt == "f32":
+                    ok = (a.double() - b.double()).abs() <= 1e-9 + 2e-6 * b.double().abs()
+                else:
+                    ok = within_ulps_of_scale(a, b, 1.0, 1e-3) | ((a.double() - b.double()).abs() <= 1e-6)
+                assert bool(ok.all()), f"{where}: {int((~ok).sum())} elements off"
+            else:
+                same = torch.equal(a.view(torch.int32 if dt == "f32" else torch.int16), b.view(torch.int32 if dt == "f32" else torch.int16))
+                if not same:
+                    # NaNs compare unequal bit-wise only through payload; require same NaN positions otherwise exact
+                    nan = a.isnan() & b.isnan()
+                    d = ulp_diff(a.reshape(-1), b.reshape(-1))
+                    d[nan.reshape(-1)] = 0
+                    assert int(d.max()) == 0, f"{where}: {int((d > 0).sum())}/{d.numel()} differ, max {int(d.max())} ulp"

@@ -94,3 +94,69 @@ def test_two_ranks_match_unsharded(split_on_tensors):
     assert sum(local_sizes) == total
     if not split_on_tensors:
         assert abs(local_sizes[0] - local_sizes[1]) <= 2 * ALIGN_ELEMS * 6
+
+
+def _ckpt_worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        g = torch.Generator().manual_seed(0)
+        shapes = [(33, 65), (129,), (1024, 3), (7,), (2000,)]
+        init = [torch.randn(s, generator=g) for s in shapes]
+        grads = [[torch.randn(s, generator=g) for s in shapes] for _ in range(6)]
+        kw = dict(lr=1e-2, weight_decay=0.1)
+
+        def step(opt, params, gs):
+            for p, gr in zip(params, gs):
+                p.grad = gr.clone()
+            opt.step()
+
+        ref_params = [torch.nn.Parameter(t.clone()) for t in init]
+        ref = torch.optim.AdamW(ref_params, **kw)
+        params = [torch.nn.Parameter(t.clone()) for t in init]
+        sharded = ShardedOptimizer(torch.optim.AdamW, params, **kw)
+        for gs in grads[:3]:
+            step(ref, ref_params, gs)
+            step(sharded, params, gs)
+        full = sharded.consolidated_state_dict()
+        want = ref.state_dict()
+        same_layout = sorted(full["state"]) == sorted(want["state"]) and all(
+            sorted(full["state"][i]) == sorted(want["state"][i]) for i in want["state"]
+        )
+        same_values = all(
+            torch.equal(torch.as_tensor(full["state"][i][k]).cpu(), torch.as_tensor(want["state"][i][k]).cpu())
+            for i in want["state"] for k in want["state"][i]
+        )
+        # the consolidated dict loads into a plain optimizer ...
+        plain_params = [torch.nn.Parameter(p.detach().clone()) for p in params]
+        plain = torch.optim.AdamW(plain_params, **kw)
+        plain.load_state_dict(full)
+        # ... and into a fresh sharded one; all three continue identically
+        params2 = [torch.nn.Parameter(p.detach().clone()) for p in params]
+        sharded2 = ShardedOptimizer(torch.optim.AdamW, params2, **kw)
+        sharded2.load_consolidated_state_dict(full)
+        for gs in grads[3:]:
+            step(ref, ref_params, gs)
+            step(plain, plain_params, gs)
+            step(sharded2, params2, gs)
+        cont = all(torch.equal(a.detach(), b.detach()) and torch.equal(a.detach(), c.detach()) for a, b, c in zip(ref_params, plain_params, params2))
+        if rank == 0:
+            out.put((same_layout, same_values, cont))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_consolidated_state_dict_round_trip():
+    ctx = mp.get_context("spawn")
+    out = ctx.SimpleQueue()
+    port = _free_port()
+    procs = [ctx.Process(target=_ckpt_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    same_layout, same_values, cont = out.get()
+    assert same_layout, "consolidated state dict has another layout than the unsharded optimizer's"
+    assert same_values, "consolidated state differs from the unsharded optimizer's"
+    assert cont, "runs continued from the consolidated checkpoint diverge"
