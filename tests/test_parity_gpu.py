@@ -145,3 +145,73 @@ def test_kernels_match_oracle_on_ragged_lists(opt, kw, dt, misalign):
             else:
                 d = ulp_diff(a.reshape(-1), b.reshape(-1))
                 assert int(d.max()) == 0, f"tensor {i} {name}: {int((d > 0).sum())}/{d.numel()} differ, max {int(d.max())} ulp"
+
+
+FUNCTIONAL = [
+    ("Adam", "adam", dict(lr=3e-4, weight_decay=1e-2), ("exp_avg", "exp_avg_sq", "kahan_comp")),
+    ("AdamW", "adamw", dict(lr=3e-4, weight_decay=1e-5, decouple_lr=True), ("exp_avg", "exp_avg_sq", "kahan_comp")),
+    ("Lion", "lion", dict(lr=1e-4, weight_decay=0.1), ("exp_avg", "kahan_comp")),
+    ("SGD", "sgd", dict(lr=1e-2, momentum=0.9, weight_decay=1e-2), ("exp_avg", "kahan_comp")),
+    ("StableAdamW", "stableadamw", dict(lr=3e-4), ("exp_avg", "exp_avg_sq", "eps_sq", "kahan_comp")),
+    ("Adan", "adan", dict(lr=3e-4, kahan_sum=True), ("exp_avg", "exp_avg_diff", "exp_avg_sq", "prev_grad", "kahan_comp")),
+    ("RAdam", "radam", dict(lr=3e-4), ("exp_avg", "exp_avg_sq", "kahan_comp")),
+    ("Ranger", "ranger", dict(lr=3e-4, k=2), ("exp_avg", "exp_avg_sq", "la_param", "kahan_comp")),
+]
+
+
+@pytest.mark.parametrize("cname,fname,kw,keys", FUNCTIONAL, ids=[f[1] for f in FUNCTIONAL])
+def test_functional_api_matches_classes(cname, fname, kw, keys):
+    """The functional entry points (lists in, same keyword set as the reference's) and the classes are
+    two doors to the same kernels: same inputs, same bits."""
+    import warnings
+
+    import optimi_b200
+
+    gen = torch.Generator().manual_seed(5)
+    shapes = [(257, 33), (4096,), (7,)]
+    host = [(torch.randn(s, generator=gen) * 0.02).to(torch.bfloat16) for s in shapes]
+    grads = [[(torch.randn(s, generator=gen) * 1e-3).to(torch.bfloat16) for s in shapes] for _ in range(4)]
+    a = [h.clone().cuda().requires_grad_(True) for h in host]
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        opt = getattr(optimi_b200, cname)(a, **kw)
+    for gs in grads:
+        for p, g in zip(a, gs):
+            p.grad = g.cuda()
+        opt.step()
+    # functional: states start as the class creates them, hyper-parameters come from the class's group
+    b = [h.clone().cuda() for h in host]
+    group = opt.param_groups[0]
+    fn = getattr(optimi_b200, fname)
+    names = {"exp_avg": "exp_avgs", "exp_avg_sq": "exp_avg_sqs", "kahan_comp": "kahan_comps", "la_param": "la_params",
+             "exp_avg_diff": "exp_avg_diffs", "prev_grad": "prev_grads", "eps_sq": "eps_sqs"}  # fmt: skip
+    states = {}
+    for k in keys:
+        if k == "la_param":
+            states[k] = [t.clone() for t in b]
+        elif k == "prev_grad":
+            states[k] = [-g.cuda() for g in grads[0]]
+        elif k == "eps_sq":
+            states[k] = [torch.tensor(group["eps"] ** 2, dtype=torch.bfloat16, device="cuda") for _ in b]
+        elif k == "kahan_comp" and not group["kahan_sum"]:
+            states[k] = None
+        else:
+            states[k] = [torch.zeros_like(t) for t in b]
+    hyper = {k: v for k, v in group.items() if k not in ("params", "setup", "step", "foreach", "triton", "gradient_release", "torch_init")}
+    if fname == "adamw":
+        hyper.pop("decouple_wd")
+    if fname == "adan":
+        hyper.pop("adam_wd", None)
+    step = torch.tensor(0, dtype=torch.int32)
+    for gs in grads:
+        kwargs = dict(hyper)
+        if fname not in ("lion", "sgd"):
+            kwargs["step"] = step
+        fn(b, [g.cuda() for g in gs], **{names[k]: v for k, v in states.items()}, **kwargs)
+    torch.cuda.synchronize()
+    for i, (p, q) in enumerate(zip(a, b)):
+        assert torch.equal(p.detach(), q), f"param {i}"
+        for k in keys:
+            if k in ("eps_sq",) or states[k] is None:
+                continue
+            assert torch.equal(opt.state[p][k], states[k][i]), f"{k} of tensor {i}"
