@@ -317,7 +317,7 @@ def run_b200_arm(args):
         step_targets = params
         sharded = None
     else:
-        sharded = ShardedOptimizer(opt_cls, params, exchange=args.exchange, **opt_kw)
+        sharded = ShardedOptimizer(opt_cls, params, exchange=args.exchange, reduce_grads=args.reduce_grads, **opt_kw)
         opt = sharded
         step_targets = sharded.shard_params
     n_local = sum(t.numel() for t in step_targets)
@@ -330,14 +330,23 @@ def run_b200_arm(args):
     else:
         piece_scale = [scales[i] for b in sharded.buckets for (i, _, _) in b["pieces"]]
     dev_grads = []
-    for t, sc in zip(step_targets, piece_scale):
-        g = torch.empty_like(t)
-        fill_grad(g, sc, gen)
-        dev_grads.append(g)
+    if args.reduce_grads:
+        # data-parallel form: every rank holds FULL gradients (its own micro-batch's) in the shared buffer and the
+        # step kernel averages them across ranks as it goes
+        sharded.attach_grads()
+        for p, sc in zip(params, scales):
+            fill_grad(p.grad, sc, gen)
+    else:
+        for t, sc in zip(step_targets, piece_scale):
+            g = torch.empty_like(t)
+            fill_grad(g, sc, gen)
+            dev_grads.append(g)
 
     def step_resident():
         if sharded is None:
             opt.step()
+        elif args.reduce_grads:
+            sharded.step()
         else:
             sharded.step(dev_grads)
 
@@ -361,7 +370,7 @@ def run_b200_arm(args):
                 opt.step()
                 ev[k][1].record(stream)
             else:
-                sharded.step_local(dev_grads)
+                sharded.step_local(None if args.reduce_grads else dev_grads)
                 ev[k][1].record(stream)
                 sharded.gather_params()
             ev[k][2].record(stream)
@@ -379,6 +388,8 @@ def run_b200_arm(args):
     value = n_params / (ms_per_step * 1e-3) / 1e9
 
     # ---- end to end: gradients from pinned host memory, result read back -----------------------
+    if args.reduce_grads:
+        dev_grads = [p.grad for p in params]  # end to end: each rank's full gradients arrive from the host
     host_grads = [torch.empty(g.shape, dtype=g.dtype, pin_memory=True) for g in dev_grads]
     for h, g in zip(host_grads, dev_grads):
         h.copy_(g)
@@ -430,8 +441,11 @@ def run_b200_arm(args):
     if sharded is not None and sharded.exchange == "push":
         # bytes this rank's step kernel stores into its peers, against the measured peer-copy rate of this pool
         pushed = 2.0 * n_local * (world - 1)
-        nvlink = {"achieved": pushed / (step_ms_max * 1e-3) / 1e9, "peak": 770.0, "unit": "GB/s per direction per GPU",
-                  "frac": pushed / (step_ms_max * 1e-3) / 1e9 / 770.0, "bytes_pushed_per_rank_per_step": pushed}
+        # with --reduce-grads the same link direction also carries the responses to the peers' gradient reads
+        pulled = pushed if args.reduce_grads else 0.0
+        nvlink = {"achieved": (pushed + pulled) / (step_ms_max * 1e-3) / 1e9, "peak": 770.0, "unit": "GB/s per direction per GPU",
+                  "frac": (pushed + pulled) / (step_ms_max * 1e-3) / 1e9 / 770.0, "bytes_pushed_per_rank_per_step": pushed,
+                  "bytes_pulled_per_rank_per_step": pulled}
 
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
@@ -443,7 +457,7 @@ def run_b200_arm(args):
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
         "config": make_config(args.workload, world, args.exchange, args.optimizer),
-        "exchange": None if sharded is None else sharded.exchange,
+        "exchange": None if sharded is None else sharded.exchange, "reduce_grads": bool(args.reduce_grads),
         "hbm_gbs": achieved, "step_ms": step_ms_max, "gather_ms": gather_ms_max, "wall_ms_per_step": t_wall * 1e3 / args.steps,
         "roofline": roofline, "nvlink": nvlink, "cpu_baseline": cpu,
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
@@ -572,6 +586,7 @@ def main():
     ap.add_argument("--workload", default="llama3-8b", choices=sorted(WORKLOADS) + ["gpt-gradient-release"])
     ap.add_argument("--optimizer", default="adamw", choices=sorted(OPTIMIZERS), help="default: the headline AdamW")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--reduce-grads", action="store_true", help="N>1 with the push exchange: also average the ranks' gradients inside the step kernel")
     ap.add_argument("--exchange", default="auto", choices=["auto", "push", "nccl"], help="N>1: how updated parameters reach the other ranks")
     args = ap.parse_args()
     if args.workload == "gpt-gradient-release":

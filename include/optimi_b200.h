@@ -77,6 +77,21 @@ int optimi_b200_adam(int n_tensors, void* const* params, void* const* grads, voi
 int optimi_b200_push_begin(int n_peers, const int64_t* peer_deltas);
 void optimi_b200_push_end(void);
 
+/* Fusing the gradient reduce-scatter of a data-parallel run into the step.  No counterpart in the
+ * reference.  Every rank keeps its own full gradient buffer in memory the other ranks can read;
+ * `grad_deltas[r]` (r < n_ranks <= 8, in rank order, 0 for the calling rank itself) is the byte
+ * distance from this rank's gradient buffer to rank r's as mapped into this process, a multiple of
+ * 16.  Between optimi_b200_pull_begin and optimi_b200_pull_end every launch the calling thread
+ * makes reads, for each element it steps, the gradient of all n_ranks ranks, adds them in fp32 in
+ * rank order, multiplies by `scale` (1/n_ranks for a mean) and rounds once to the storage type;
+ * that value is the gradient the optimizer sees.  It exists only in registers; no rank's buffer is
+ * written.  The kernels wait for nobody: the caller orders the ranks before the launch (all
+ * gradients complete) and after it (before any gradient buffer is overwritten).  Combine with
+ * optimi_b200_push_begin for reduce-scatter + step + all-gather in one kernel.  Not available for
+ * StableAdamW (its launches are rejected while a pull is active). */
+int optimi_b200_pull_begin(int n_ranks, const int64_t* grad_deltas, double scale);
+void optimi_b200_pull_end(void);
+
 /* Lion.  Replaces _foreach_lion (optimi/lion.py:341-380), _single_param_lion (optimi/lion.py:301-338)
  * and the Triton launchers (optimi/lion.py:453-530).  `weight_decay` is the folded factor
  * (optimi/lion.py:227-231), 0 for none. */

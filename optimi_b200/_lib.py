@@ -35,7 +35,7 @@ SIGNATURES = {
     "optimi_b200_radam": [_I] + [_P] * 5 + [_P, _I] + [_D] * 6 + [_I, _D] + [_I] * 3 + [_P],
     "optimi_b200_ranger": [_I] + [_P] * 6 + [_P, _I] + [_D] * 6 + [_I, _D, _I, _D] + [_I] * 3 + [_P],
 }
-EXPORTS = list(SIGNATURES) + ["optimi_b200_push_begin", "optimi_b200_push_end", "optimi_b200_last_error", "optimi_b200_version", "optimi_b200_launch_count", "optimi_b200_stableadamw_workspace_bytes"]
+EXPORTS = list(SIGNATURES) + ["optimi_b200_push_begin", "optimi_b200_push_end", "optimi_b200_pull_begin", "optimi_b200_pull_end", "optimi_b200_last_error", "optimi_b200_version", "optimi_b200_launch_count", "optimi_b200_stableadamw_workspace_bytes"]
 
 
 def _load() -> ctypes.CDLL:
@@ -55,6 +55,10 @@ def _load() -> ctypes.CDLL:
     lib.optimi_b200_push_begin.argtypes = [_I, _P]
     lib.optimi_b200_push_end.restype = None
     lib.optimi_b200_push_end.argtypes = []
+    lib.optimi_b200_pull_begin.restype = _I
+    lib.optimi_b200_pull_begin.argtypes = [_I, _P, _D]
+    lib.optimi_b200_pull_end.restype = None
+    lib.optimi_b200_pull_end.argtypes = []
     lib.optimi_b200_launch_count.restype = ctypes.c_ulonglong
     lib.optimi_b200_launch_count.argtypes = []
     lib.optimi_b200_stableadamw_workspace_bytes.restype = ctypes.c_size_t
@@ -79,6 +83,21 @@ class peer_push:
 
     def __exit__(self, *exc):
         LIB.optimi_b200_push_end()
+
+
+class peer_pull:
+    """Context manager: launches made by this thread inside it take as gradient the scaled fp32 sum of
+    all ranks' gradient buffers (`deltas`: byte offsets to them in rank order, 0 for this rank)."""
+
+    def __init__(self, deltas, scale: float):
+        self.deltas, self.scale = (ctypes.c_int64 * len(deltas))(*deltas), scale
+
+    def __enter__(self):
+        check(LIB.optimi_b200_pull_begin(len(self.deltas), ctypes.cast(self.deltas, ctypes.c_void_p), self.scale))
+        return self
+
+    def __exit__(self, *exc):
+        LIB.optimi_b200_pull_end()
 
 
 def check(rc: int) -> None:

@@ -214,6 +214,57 @@ __device__ __forceinline__ void push_one(const PeerPush& push, T* local, T v) {
   for (int j = 0; j < push.n; j++) *reinterpret_cast<T*>(reinterpret_cast<char*>(local) + push.delta[j]) = v;
 }
 
+// Peer pull: the fused form of "reduce-scatter the gradients, then step".  Every rank keeps its own
+// full gradient buffer in memory the others can read; `delta[r]` is the byte distance from this
+// rank's buffer to rank r's (0 for this rank itself), for r = 0..n-1 in rank order.  A block loads
+// the gradient vector of its tile from all n ranks (all loads issued before the first is used), adds
+// them in fp32 in rank order, multiplies by `scale` (1/n for a mean) and rounds once to the storage
+// type; the optimizer's arithmetic then sees that value as its gradient.  The reduced gradient
+// exists only in registers.  Plain peer loads, no waits on other ranks inside the kernel: the caller
+// orders the ranks before the launch (their gradients must be complete) and after it (before the
+// buffers are overwritten).
+constexpr int kMaxRanks = 8;
+struct PeerPull {
+  int n;
+  float scale;
+  long long delta[kMaxRanks];
+};
+template <typename T> struct Pack;  // defined above
+// NR = compile-time bound on the ranks (2, 4 or 8): it sizes the registers that hold the vectors in
+// flight, and with them how many blocks fit on an SM — few ranks need many resident threads to keep
+// NVLink busy, many ranks need few.
+template <typename T, int NR>
+__device__ __forceinline__ uint4 pull_vec(const PeerPull& pull, const T* local) {
+  constexpr int N = VecN<T>::N;
+  uint4 raw[NR];
+#pragma unroll
+  for (int r = 0; r < NR; r++)
+    if (r < pull.n) raw[r] = *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(local) + pull.delta[r]);
+  float acc[N];
+  Pack<T>::unpack(raw[0], acc);
+#pragma unroll
+  for (int r = 1; r < NR; r++) {
+    if (r < pull.n) {
+      float x[N];
+      Pack<T>::unpack(raw[r], x);
+#pragma unroll
+      for (int j = 0; j < N; j++) acc[j] = __fadd_rn(acc[j], x[j]);
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < N; j++) acc[j] = rnd<T>(__fmul_rn(acc[j], pull.scale));
+  return Pack<T>::pack(acc);
+}
+template <typename T>
+__device__ __forceinline__ float pull_one(const PeerPull& pull, const T* local) {
+  float acc = 0.f;
+  for (int r = 0; r < pull.n; r++) {
+    const float x = Pack<T>::load1(reinterpret_cast<const T*>(reinterpret_cast<const char*>(local) + pull.delta[r]));
+    acc = r == 0 ? x : __fadd_rn(acc, x);
+  }
+  return rnd<T>(__fmul_rn(acc, pull.scale));
+}
+
 // ---------------------------------------------------------------------------------------------
 // Generic element-wise machinery.  An Op describes one optimizer variant:
 //   NL, U                     number of tensor lists, vectors per thread per list in a full tile
@@ -225,6 +276,8 @@ __device__ __forceinline__ void push_one(const PeerPush& push, T* local, T v) {
 //   kSumSlot                  index of an e[] slot whose values compute_vec sums up (-1: none)
 //   kMinBlocks                blocks that must fit on one SM (register cap for the compiler)
 //   kPush                     also store updated parameters into the peers' copies (Args has .push)
+//   kPull                     0, or the rank bound (2/4/8) of a launch whose gradients are the scaled sum of all
+//                             ranks' gradient buffers (Args has .pull)
 // ---------------------------------------------------------------------------------------------
 struct NoCtx {};
 
@@ -233,8 +286,15 @@ template <int NL> struct Vecs { uint4 r[NL]; };
 template <typename T, class Op>
 __device__ __forceinline__ void load_vec(Vecs<Op::NL>& v, T* const (&p)[Op::NL], int i, const typename Op::Args& a) {
 #pragma unroll
-  for (int l = 0; l < Op::NL; l++)
+  for (int l = 0; l < Op::NL; l++) {
+    if constexpr (Op::kPull) {  // list 1 is the gradient list in every op that can pull
+      if (l == 1) {
+        v.r[1] = pull_vec<T, Op::kPull>(a.pull, p[1] + i);
+        continue;
+      }
+    }
     if (Op::reads(l, a)) v.r[l] = ldv(p[l] + i);
+  }
 }
 
 template <typename T, class Op>
@@ -283,6 +343,7 @@ __device__ __forceinline__ float scalar_elem(T* const (&p)[Op::NL], int i, const
   float e[Op::NL];
 #pragma unroll
   for (int l = 0; l < Op::NL; l++) e[l] = Op::reads(l, a) ? Pack<T>::load1(p[l] + i) : 0.f;
+  if constexpr (Op::kPull) e[1] = pull_one<T>(a.pull, p[1] + i);
   Op::template elem<T>(e, a, ctx);
 #pragma unroll
   for (int l = 0; l < Op::NL; l++)

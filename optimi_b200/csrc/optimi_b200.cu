@@ -128,18 +128,35 @@ static int launch_op(const char* name, int n, const int64_t* numels, void* const
   });
 }
 
-// Peer push requested for the calling thread's next launches (optimi_b200_push_begin / _end).
+// Peer push / pull requested for the calling thread's next launches (optimi_b200_push_begin,
+// optimi_b200_pull_begin and their _end).
 static thread_local PeerPush g_push = {0, {0}};
+static thread_local PeerPull g_pull = {0, 1.0f, {0}};
 
-// Launches Op, or PushOp<Op> when a peer push is active.
-template <typename T, class Op>
+// Launches Op, or PeerOp<Op, ...> when a peer push and/or pull is active.  PULLABLE is false for the
+// ops without a gradient list at position 1 (StableAdamW's passes).
+template <typename T, class Op, bool PULLABLE = true>
 static int launch_maybe_push(const char* name, int n, const int64_t* numels, void* const* const (&lists)[Op::NL],
                              const typename Op::Args& args, cudaStream_t stream) {
+  if (g_pull.n > 0) {
+    if constexpr (PULLABLE) {
+      PeerArgs<typename Op::Args> pa;
+      pa.base = args;
+      pa.push = g_push;
+      pa.pull = g_pull;
+      if (g_pull.n <= 2) return launch_op<T, PeerOp<Op, 2>>(name, n, numels, lists, pa, stream);
+      if (g_pull.n <= 4) return launch_op<T, PeerOp<Op, 4>>(name, n, numels, lists, pa, stream);
+      return launch_op<T, PeerOp<Op, 8>>(name, n, numels, lists, pa, stream);
+    } else {
+      return fail(OPTIMI_ERR_INVALID_ARGUMENT, "%s: the gradient pull is not available for this optimizer", name);
+    }
+  }
   if (g_push.n > 0) {
-    PushArgs<typename Op::Args> pa;
+    PeerArgs<typename Op::Args> pa;
     pa.base = args;
     pa.push = g_push;
-    return launch_op<T, PushOp<Op>>(name, n, numels, lists, pa, stream);
+    pa.pull.n = 0;
+    return launch_op<T, PeerOp<Op, 0>>(name, n, numels, lists, pa, stream);
   }
   return launch_op<T, Op>(name, n, numels, lists, args, stream);
 }
@@ -294,9 +311,9 @@ static int stableadamw_typed(int n, void* const* params, void* const* grads, voi
   ua.has_wd = weight_decay != 0;
   void* const* const lists_b[4] = {params, exp_avgs, exp_avg_sqs, kahan ? kahan_comps : nullptr};
   if constexpr (sizeof(T) == 2) {  // Kahan compensation exists for the 16-bit storage types only
-    if (kahan) return launch_maybe_push<T, StableUpdateOp<true>>("optimi_b200_stableadamw (update)", n, numels, lists_b, ua, stream);
+    if (kahan) return launch_maybe_push<T, StableUpdateOp<true>, false>("optimi_b200_stableadamw (update)", n, numels, lists_b, ua, stream);
   }
-  return launch_maybe_push<T, StableUpdateOp<false>>("optimi_b200_stableadamw (update)", n, numels, lists_b, ua, stream);
+  return launch_maybe_push<T, StableUpdateOp<false>, false>("optimi_b200_stableadamw (update)", n, numels, lists_b, ua, stream);
 }
 
 static int wd_mode_of(double weight_decay, int decouple_wd) {
@@ -328,6 +345,20 @@ int optimi_b200_push_begin(int n_peers, const int64_t* peer_deltas) {
 }
 
 void optimi_b200_push_end(void) { g_push.n = 0; }
+
+int optimi_b200_pull_begin(int n_ranks, const int64_t* grad_deltas, double scale) {
+  const char* fn = "optimi_b200_pull_begin";
+  if (n_ranks < 0 || n_ranks > kMaxRanks) return fail(OPTIMI_ERR_INVALID_ARGUMENT, "%s: n_ranks=%d is outside 0..%d", fn, n_ranks, kMaxRanks);
+  if (n_ranks > 0 && !grad_deltas) return fail(OPTIMI_ERR_INVALID_ARGUMENT, "%s: grad_deltas is NULL", fn);
+  for (int r = 0; r < n_ranks; r++)
+    if (grad_deltas[r] % 16) return fail(OPTIMI_ERR_INVALID_ARGUMENT, "%s: grad_deltas[%d] is not a multiple of 16 bytes", fn, r);
+  g_pull.n = n_ranks;
+  g_pull.scale = (float)scale;
+  for (int r = 0; r < kMaxRanks; r++) g_pull.delta[r] = r < n_ranks ? (long long)grad_deltas[r] : 0;
+  return OPTIMI_OK;
+}
+
+void optimi_b200_pull_end(void) { g_pull.n = 0; }
 
 unsigned long long optimi_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 

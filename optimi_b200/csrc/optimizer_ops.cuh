@@ -70,6 +70,7 @@ struct OpBase {
 #endif
   static constexpr int kMinBlocks = OPTIMI_MIN_BLOCKS;  // 10: <= 51 registers per thread at 128 threads
   static constexpr bool kPush = false;
+  static constexpr int kPull = 0;
   template <class Table, class Args>
   static __device__ __forceinline__ NoCtx context(const Table&, const Span&, const Args&) { return NoCtx{}; }
 };
@@ -107,19 +108,30 @@ struct AdamOp : OpBase {
   }
 };
 
-// Any op whose list 0 is the parameter list, with the peer push added to its stores.
+// Any op whose list 0 is the parameter list and list 1 the gradient list, with the peer push added
+// to its stores and, when PULL, the gradient replaced by the scaled sum over all ranks' gradients.
 template <class BaseArgs>
-struct PushArgs {
+struct PeerArgs {
   BaseArgs base;
   PeerPush push;
+  PeerPull pull;
 };
 
-template <class Base>
-struct PushOp {
+template <class Base, int PULL>  // PULL: 0 = push only, else the rank bound 2, 4 or 8
+struct PeerOp {
   static constexpr int NL = Base::NL, U = Base::U, kSumSlot = Base::kSumSlot;
-  static constexpr int kMinBlocks = Base::kMinBlocks > 2 ? Base::kMinBlocks - 2 : 1;
+  // Remote loads take microseconds: what keeps NVLink busy is many resident threads, each with its
+  // gradient vectors in flight (two vectors per thread at half the residency was measured slower;
+  // beyond ~900 resident threads per SM nothing is gained: the link direction that carries both the
+  // peers' pushes and this rank's read responses is then the limit).  The register cap loosens as
+  // the rank bound, and with it the vectors held, grows.
+  static constexpr int kMinBlocks = PULL == 0 ? (Base::kMinBlocks > 2 ? Base::kMinBlocks - 2 : 1)
+                                    : PULL == 2 ? (Base::kMinBlocks > 3 ? Base::kMinBlocks - 3 : 1)
+                                    : PULL == 4 ? (Base::kMinBlocks > 4 ? Base::kMinBlocks - 4 : 1)
+                                                : (Base::kMinBlocks > 5 ? Base::kMinBlocks - 5 : 1);
   static constexpr bool kPush = true;
-  using Args = PushArgs<typename Base::Args>;
+  static constexpr int kPull = PULL;
+  using Args = PeerArgs<typename Base::Args>;
   using Ctx = typename Base::Ctx;
   template <class Table>
   static __device__ __forceinline__ Ctx context(const Table& tab, const Span& s, const Args& a) { return Base::context(tab, s, a.base); }
@@ -357,6 +369,7 @@ struct StableUpdateOp {
   static constexpr int kSumSlot = -1;
   static constexpr int kMinBlocks = 10;
   static constexpr bool kPush = false;
+  static constexpr int kPull = 0;
   using Args = StableUpdateArgs;
   using Ctx = float2;
   template <class Table>

@@ -21,6 +21,13 @@ Exchange modes (`exchange=`):
              CUDA ranks and one parameter dtype; anything else falls back to "nccl".
     "auto"   "push" when available, else "nccl".
 
+`reduce_grads=True` (with the push exchange) also folds the data-parallel gradient reduction into the
+step: gradients live in a second symmetric flat buffer (`attach_grads()` points every `p.grad` into it,
+so autograd accumulates there), and the step kernel reads, for each element of its range, the gradient
+of every rank over NVLink, averages them in fp32 in rank order and rounds once — reduce-scatter, step
+and all-gather in one launch, with one tiny collective before it (all gradients written) and one
+after it (all reads and pushes done).  Not available for StableAdamW.
+
 Sharded and unsharded runs produce bit-identical parameters: each element sees exactly the same
 arithmetic, only on another GPU.
 """
@@ -93,7 +100,7 @@ class ShardedOptimizer:
     """
 
     def __init__(self, optimizer_cls: Callable, params, process_group=None, split_on_tensors: bool | None = None,
-                 gather: str | Callable = "nccl", exchange: str = "nccl", **kwargs: Any):  # fmt: skip
+                 gather: str | Callable = "nccl", exchange: str = "nccl", reduce_grads: bool = False, **kwargs: Any):  # fmt: skip
         self.group = process_group
         self.rank = dist.get_rank(process_group) if dist.is_initialized() else 0
         self.world = dist.get_world_size(process_group) if dist.is_initialized() else 1
@@ -110,6 +117,10 @@ class ShardedOptimizer:
         self.exchange = "push" if (exchange in ("push", "auto") and can_push) else "nccl"
         self._peer_deltas: list[int] | None = None
         self._symm_handles = []
+        if reduce_grads and (self.exchange != "push" or split_on_tensors):
+            raise ValueError("reduce_grads=True needs the push exchange and an optimizer other than StableAdamW")
+        self.reduce_grads = reduce_grads
+        self._grad_deltas: list[int] | None = None
 
         # one flat buffer per (device, dtype)
         self.buckets: list[dict[str, Any]] = []
@@ -119,8 +130,13 @@ class ShardedOptimizer:
         shard_params: list[Tensor] = []
         for (device, dtype), plist in groups.items():
             layout = FlatLayout([p.numel() for p in plist], self.world, split_on_tensors)
+            grad_flat = grad_handle = None
             if self.exchange == "push":
-                flat = self._symmetric_buffer(layout.total, dtype, device)
+                flat, _, self._peer_deltas = self._symmetric_buffer(layout.total, dtype, device)
+                if reduce_grads:
+                    grad_flat, grad_handle, others = self._symmetric_buffer(layout.total, dtype, device)
+                    others = iter(others)  # all ranks in rank order, 0 for this one
+                    self._grad_deltas = [0 if r == self.rank else next(others) for r in range(self.world)]
             else:
                 flat = torch.zeros(layout.total, dtype=dtype, device=device)
             for p, off in zip(plist, layout.offsets):
@@ -133,7 +149,8 @@ class ShardedOptimizer:
                 sp = torch.nn.Parameter(plist[i].data.view(-1)[a:b], requires_grad=True)
                 shards.append(sp)
             shard_params.extend(shards)
-            self.buckets.append(dict(layout=layout, flat=flat, params=plist, pieces=pieces, shards=shards))
+            self.buckets.append(dict(layout=layout, flat=flat, params=plist, pieces=pieces, shards=shards, grad_flat=grad_flat,
+                                     grad_handle=grad_handle))
         self.shard_params = shard_params
         self.inner = optimizer_cls(shard_params, **kwargs)
         if self.exchange == "push":
@@ -142,9 +159,10 @@ class ShardedOptimizer:
             torch.cuda.synchronize(self.params[0].device)
             dist.barrier(self.group)
 
-    def _symmetric_buffer(self, numel: int, dtype: torch.dtype, device: torch.device) -> Tensor:
-        """A zeroed buffer every rank of the group can store into: torch symmetric memory (CUDA virtual
-        memory handles exchanged between the ranks).  Only plain peer stores are used on it."""
+    def _symmetric_buffer(self, numel: int, dtype: torch.dtype, device: torch.device):
+        """A zeroed buffer every rank of the group can load from and store into: torch symmetric memory
+        (CUDA virtual memory handles exchanged between the ranks); only plain peer loads and stores are
+        used on it.  Returns (buffer, handle, byte offsets from this rank's buffer to each peer's)."""
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm
 
@@ -155,11 +173,11 @@ class ShardedOptimizer:
         ptrs = list(handle.buffer_ptrs)
         if ptrs[self.rank] != base:
             raise RuntimeError("symmetric memory: this rank's buffer pointer does not match the allocation")
-        self._peer_deltas = [ptrs[r] - base for r in range(self.world) if r != self.rank]
+        deltas = [ptrs[r] - base for r in range(self.world) if r != self.rank]
         self._symm_handles.append(handle)
         torch.cuda.synchronize(device)
         dist.barrier(self.group)
-        return flat
+        return flat, handle, deltas
 
     # convenience passthroughs ------------------------------------------------------------------
     @property
@@ -173,7 +191,25 @@ class ShardedOptimizer:
     def local_elements(self) -> int:
         return sum(sp.numel() for sp in self.shard_params)
 
+    def attach_grads(self) -> None:
+        """reduce_grads only: points every parameter's `.grad` at its (zeroed) slot of the shared gradient
+        buffer, so that the backward pass accumulates where the other ranks' step kernels can read."""
+        for b in self.buckets:
+            gf, layout = b["grad_flat"], b["layout"]
+            for p, off in zip(b["params"], layout.offsets):
+                p.grad = gf[off : off + p.numel()].view(p.shape)
+
     def _bind_grads(self):
+        if self.reduce_grads:
+            for b in self.buckets:
+                gf, layout = b["grad_flat"], b["layout"]
+                for (i, a, e), sp in zip(b["pieces"], b["shards"]):
+                    g = b["params"][i].grad
+                    off = layout.offsets[i]
+                    if g is None or g.data_ptr() != gf.data_ptr() + off * gf.element_size():
+                        raise RuntimeError("reduce_grads=True: call attach_grads() before the backward pass (gradients must live in the shared buffer)")
+                    sp.grad = gf[off + a : off + e]
+            return
         for b in self.buckets:
             for (i, a, e), sp in zip(b["pieces"], b["shards"]):
                 g = b["params"][i].grad
@@ -195,12 +231,45 @@ class ShardedOptimizer:
             for sp, g in zip(self.shard_params, shard_grads):
                 sp.grad = g
         if self.exchange == "push":
-            from ._lib import peer_push
+            from ._lib import peer_pull, peer_push
 
-            with peer_push(self._peer_deltas):
-                self.inner.step()
+            if self.reduce_grads:
+                if shard_grads is not None:
+                    raise ValueError("reduce_grads=True reads the gradients of the shared buffer; do not pass shard_grads")
+                dist.all_reduce(self._meet, group=self.group)  # every rank's gradients are written
+                self._init_states_from_mean_gradients()
+                with peer_pull(self._grad_deltas, 1.0 / self.world), peer_push(self._peer_deltas):
+                    self.inner.step()
+            else:
+                with peer_push(self._peer_deltas):
+                    self.inner.step()
         else:
             self.inner.step()
+
+    def _init_states_from_mean_gradients(self) -> None:
+        """reduce_grads, first step only.  Some optimizers seed their state from the first gradient
+        (Adan's previous gradient, SGD's `torch_init` momentum); the fused step never materialises the
+        averaged gradient, so it is computed here once, with the kernel's own arithmetic (fp32 sum in
+        rank order, times 1/world, one rounding), just for the state constructors."""
+        if getattr(self, "_states_seeded", False) or not hasattr(self.inner, "_init_state"):
+            return
+        self._states_seeded = True
+        torch.cuda.current_stream().synchronize()  # the meeting collective above has completed: all gradients are in place
+        group = self.inner.param_groups[0]
+        for b in self.buckets:
+            layout, gf, handle = b["layout"], b["grad_flat"], b["grad_handle"]
+            views = [handle.get_buffer(r, (layout.total,), gf.dtype) if r != self.rank else gf for r in range(self.world)]
+            for (i, a, e), sp in zip(b["pieces"], b["shards"]):
+                lo = layout.offsets[i] + a
+                acc = views[0][lo : lo + e - a].float()
+                for v in views[1:]:
+                    acc = acc + v[lo : lo + e - a].float()
+                bound = sp.grad
+                sp.grad = (acc * (1.0 / self.world)).to(gf.dtype)
+                self.inner._init_state(group, self.inner.state[sp], sp)
+                sp.grad = bound
+        torch.cuda.synchronize()
+        dist.barrier(self.group)
 
     @torch.no_grad()
     def gather_params(self):
@@ -235,6 +304,10 @@ class ShardedOptimizer:
         self.gather_params()
 
     def zero_grad(self, set_to_none: bool = True):
+        if self.reduce_grads:  # gradients stay attached to the shared buffer; call after step() (its closing collective
+            for b in self.buckets:  # guarantees no rank is still reading)
+                b["grad_flat"].zero_()
+            return
         for p in self.params:
             if p.grad is not None:
                 if set_to_none:

@@ -79,3 +79,64 @@ def test_sharded_step_equals_unsharded(cname, kw, exchange):
         p.join(180)
         assert p.exitcode == 0
     assert out.get(), "sharded parameters differ from the unsharded run"
+
+
+def _reduce_worker(rank, world, port, cname, kw, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        import optimi_b200
+        from optimi_b200.zero import ShardedOptimizer
+
+        dev = torch.device("cuda", rank)
+        g = torch.Generator().manual_seed(0)
+        shapes = [(257, 129), (4096,), (1000, 333), (7,), (65536,), (300, 1024)]
+        host = [(torch.randn(s, generator=g) * 0.02).to(torch.bfloat16) for s in shapes]
+        params = [torch.nn.Parameter(h.clone().to(dev)) for h in host]
+        ref = [torch.nn.Parameter(h.clone().to(dev)) for h in host]
+        cls = getattr(optimi_b200, cname)
+        sharded = ShardedOptimizer(cls, params, exchange="push", reduce_grads=True, **kw)
+        plain = cls(ref, **kw)
+        for _ in range(4):
+            # every rank draws the gradients of ALL ranks (same generator), keeps its own, and the
+            # unsharded run steps with their fp32 mean rounded once
+            per_rank = [[(torch.randn(s, generator=g) * 1e-3).to(torch.bfloat16) for s in shapes] for _ in range(world)]
+            sharded.attach_grads()
+            for p, gr in zip(params, per_rank[rank]):
+                p.grad.copy_(gr.to(dev))
+            for i, r in enumerate(ref):
+                acc = per_rank[0][i].float()
+                for other in per_rank[1:]:
+                    acc = acc + other[i].float()
+                r.grad = (acc * (1.0 / world)).to(torch.bfloat16).to(dev)
+            sharded.step()
+            plain.step()
+            sharded.zero_grad()
+        torch.cuda.synchronize()
+        ok = all(torch.equal(p.detach(), r.detach()) for p, r in zip(params, ref))
+        oks = [None] * world
+        dist.all_gather_object(oks, ok)
+        if rank == 0:
+            out.put(all(oks))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("cname,kw", [("AdamW", dict(lr=3e-4, weight_decay=1e-5, decouple_lr=True)), ("Lion", dict(lr=1e-4)),
+                                      ("Adan", dict(lr=3e-4, kahan_sum=True))])  # fmt: skip
+def test_fused_gradient_mean_step_and_exchange(cname, kw):
+    """reduce-scatter + step + all-gather in one kernel: equals an unsharded step on the mean gradient."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world = 2
+    ctx = mp.get_context("spawn")
+    out = ctx.SimpleQueue()
+    port = _free_port()
+    procs = [ctx.Process(target=_reduce_worker, args=(r, world, port, cname, kw, out)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(180)
+        assert p.exitcode == 0
+    assert out.get(), "fused gradient mean + step differs from the unsharded run on the mean gradient"
