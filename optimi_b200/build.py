@@ -23,7 +23,7 @@ LIB = os.path.join(LIB_DIR, "liboptimi_b200.so")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-fmad=false", "-prec-div=true",
-    "-prec-sqrt=true", "-ftz=false", "-shared", "-Xcompiler", "-fPIC", "-Xcompiler", "-O2", "--use-local-env",
+    "-prec-sqrt=true", "-ftz=false", "-Xcompiler", "-fPIC", "-Xcompiler", "-O2",
 ]  # fmt: skip
 
 
@@ -53,23 +53,36 @@ def up_to_date() -> bool:
         return fh.read().strip() == source_hash()
 
 
+N_PARTS = 3  # the source compiles as independent translation units (OPTIMI_PART), built in parallel
+
+
 def build(force: bool = False, verbose: bool = False) -> str:
     if not force and up_to_date():
         return LIB
     os.makedirs(LIB_DIR, exist_ok=True)
-    cmd = [find_nvcc(), *[f for f in NVCC_FLAGS if f != "--use-local-env"], "-o", LIB, SRC]
-    if verbose:
-        cmd.insert(1, "-Xptxas")
-        cmd.insert(2, "-v")
-    env = dict(os.environ)
-    # the image exports CC/CXX pointing at a wrapper; let nvcc use the system host compiler
-    if os.path.exists("/usr/bin/g++"):
-        cmd[1:1] = ["-ccbin", "/usr/bin/g++"]
-    res = subprocess.run(cmd, env=env, capture_output=True, text=True)
+    nvcc = find_nvcc()
+    ccbin = ["-ccbin", "/usr/bin/g++"] if os.path.exists("/usr/bin/g++") else []  # the image's CC/CXX point at a wrapper
+    compile_flags = [f for f in NVCC_FLAGS if f not in ("-shared", "--use-local-env")]
+    objs, procs = [], []
+    for part in range(N_PARTS):
+        obj = os.path.join(LIB_DIR, f"part{part}.o")
+        objs.append(obj)
+        cmd = [nvcc, *ccbin, *compile_flags, *(["-Xptxas", "-v"] if verbose else []), f"-DOPTIMI_PART={part}", "-c", "-o", obj, SRC]
+        procs.append((cmd, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)))
+    log = ""
+    for cmd, p in procs:
+        out, err = p.communicate()
+        log += out + err
+        if p.returncode != 0:
+            raise RuntimeError("nvcc failed:\n" + " ".join(cmd) + "\n" + out + err)
+    link = [nvcc, *ccbin, "-shared", "-o", LIB, *objs]
+    res = subprocess.run(link, capture_output=True, text=True)
     if res.returncode != 0:
-        raise RuntimeError("nvcc failed:\n" + " ".join(cmd) + "\n" + res.stdout + res.stderr)
+        raise RuntimeError("link failed:\n" + " ".join(link) + "\n" + res.stdout + res.stderr)
+    for obj in objs:
+        os.remove(obj)
     if verbose:
-        print(res.stderr)
+        print(log)
     with open(STAMP, "w") as fh:
         fh.write(source_hash())
     return LIB

@@ -18,7 +18,20 @@ namespace optimi {
 // ---------------------------------------------------------------------------------------------
 // errors
 // ---------------------------------------------------------------------------------------------
-static thread_local char g_error[512] = "";
+// The library may be compiled as one translation unit or as several in parallel (OPTIMI_PART = 0, 1, 2:
+// see optimi_b200/build.py); part 0 owns the process-wide state, the others refer to it.
+#define COMMA ,
+#if defined(OPTIMI_PART) && OPTIMI_PART != 0
+#define OPTIMI_SHARED(decl, init) extern decl
+#else
+#define OPTIMI_SHARED(decl, init) decl init
+#endif
+#if defined(OPTIMI_PART)
+#define OPTIMI_IN_PART(p) (OPTIMI_PART == (p))
+#else
+#define OPTIMI_IN_PART(p) 1
+#endif
+OPTIMI_SHARED(thread_local char g_error[512], = "");
 
 static int fail(int code, const char* fmt, ...) {
   va_list ap;
@@ -28,7 +41,7 @@ static int fail(int code, const char* fmt, ...) {
   return code;
 }
 
-static std::atomic<unsigned long long> g_launches{0};
+OPTIMI_SHARED(std::atomic<unsigned long long> g_launches, {0});
 
 static int check_launch(const char* what) {
   g_launches.fetch_add(1, std::memory_order_relaxed);
@@ -130,8 +143,8 @@ static int launch_op(const char* name, int n, const int64_t* numels, void* const
 
 // Peer push / pull requested for the calling thread's next launches (optimi_b200_push_begin,
 // optimi_b200_pull_begin and their _end).
-static thread_local PeerPush g_push = {0, {0}};
-static thread_local PeerPull g_pull = {0, 1.0f, {0}};
+OPTIMI_SHARED(thread_local PeerPush g_push, = {0 COMMA {0}});
+OPTIMI_SHARED(thread_local PeerPull g_pull, = {0 COMMA 1.0f COMMA {0}});
 
 // Launches Op, or PeerOp<Op, ...> when a peer push and/or pull is active.  PULLABLE is false for the
 // ops without a gradient list at position 1 (StableAdamW's passes).
@@ -329,6 +342,7 @@ using namespace optimi;
 
 extern "C" {
 
+#if OPTIMI_IN_PART(0)
 const char* optimi_b200_last_error(void) { return g_error; }
 
 int optimi_b200_version(void) { return 100; }
@@ -384,6 +398,9 @@ int optimi_b200_adam(int n, void* const* params, void* const* grads, void* const
   return dispatch<AdamOp>("optimi_b200_adam", dtype, kahan, update, n, numels, lists, a, (cudaStream_t)stream);
 }
 
+#endif  // part 0 (continues below with lion and sgd)
+
+#if OPTIMI_IN_PART(1)
 int optimi_b200_radam(int n, void* const* params, void* const* grads, void* const* exp_avgs, void* const* exp_avg_sqs,
                       void* const* kahan_comps, const int64_t* numels, int dtype, double lr, double beta1_comp,
                       double beta2_hat, double beta2_comp, double weight_decay, double eps, int use_rect, double rect,
@@ -423,6 +440,9 @@ int optimi_b200_ranger(int n, void* const* params, void* const* grads, void* con
   return dispatch<RadamOp>(fn, dtype, kahan, update, n, numels, lists, a, (cudaStream_t)stream);
 }
 
+#endif  // part 1 (continues below with adan)
+
+#if OPTIMI_IN_PART(0)
 int optimi_b200_lion(int n, void* const* params, void* const* grads, void* const* exp_avgs, void* const* kahan_comps,
                      const int64_t* numels, int dtype, double lr, double beta1_comp, double beta2_comp, double weight_decay,
                      int kahan_sum, int update_parameters, void* stream) {
@@ -465,6 +485,9 @@ int optimi_b200_sgd(int n, void* const* params, void* const* grads, void* const*
   return dispatch<SgdOp>("optimi_b200_sgd", dtype, kahan, update, n, numels, lists, a, (cudaStream_t)stream);
 }
 
+#endif  // part 0
+
+#if OPTIMI_IN_PART(1)
 int optimi_b200_adan(int n, void* const* params, void* const* grads, void* const* exp_avgs, void* const* exp_avg_diffs,
                      void* const* exp_avg_sqs, void* const* prev_grads, void* const* kahan_comps, const int64_t* numels,
                      int dtype, double lr, double beta1_comp, double beta2, double beta2_comp, double beta3_hat,
@@ -493,6 +516,9 @@ int optimi_b200_adan(int n, void* const* params, void* const* grads, void* const
   return dispatch<AdanOp>("optimi_b200_adan", dtype, kahan, update, n, numels, lists, a, (cudaStream_t)stream);
 }
 
+#endif  // part 1
+
+#if OPTIMI_IN_PART(2)
 size_t optimi_b200_stableadamw_workspace_bytes(int n, const int64_t* numels) {
   if (n <= 0 || !numels) return 16;
   // the float32 tile is the smallest, so this bounds every storage type
@@ -531,8 +557,11 @@ int optimi_b200_stableadamw(int n, void* const* params, void* const* grads, void
   }
 }
 
+#endif  // part 2 (continues below with the static-scratch variant)
+
 }  // extern "C"
 
+#if OPTIMI_IN_PART(2)
 // ---------------------------------------------------------------------------------------------
 // StableAdamW without any caller-provided scratch
 // ---------------------------------------------------------------------------------------------
@@ -616,3 +645,4 @@ extern "C" int optimi_b200_stableadamw_static(int n, void* const* params, void* 
                                        beta2_comp, weight_decay, eps, decouple_lr, max_lr, kahan, update, scratch, cap, s);
   }
 }
+#endif  // part 2
