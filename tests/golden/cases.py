@@ -174,3 +174,27 @@ def make_inputs(case: Case):
 def accumulate_on(step_index: int) -> bool:
     """Gradient-release cases: iterations 0,1,2 of every four only accumulate into the states."""
     return step_index % 4 != 3
+
+
+# ------------------------------------------------------------------------------------------------
+# BASELINE configuration 1: AdamW float32 on the parameters of a 2-layer MLP (Linear 1024->4096 + bias,
+# Linear 4096->1024 + bias, 8 393 728 parameters), weights ~N(0, 0.02^2), biases 0, fresh gradients
+# ~N(0, (1e-3)^2) every step from seed 0, lr 1e-3, betas (0.9, 0.99), eps 1e-6, weight decay 1e-2 (decoupled),
+# 20 steps.  Too large to store: the golden keeps every 997th element of each result tensor.
+# ------------------------------------------------------------------------------------------------
+CONFIG1_SHAPES = [(4096, 1024), (4096,), (1024, 4096), (1024,)]
+CONFIG1_HYPER = dict(lr=1e-3, betas=(0.9, 0.99), eps=1e-6, weight_decay=1e-2, decouple_lr=False)
+CONFIG1_STEPS = 20
+CONFIG1_STRIDE = 997
+
+
+def config1_params():
+    rng = np.random.default_rng(0)
+    return [(rng.standard_normal(s) * 0.02).astype(np.float32) if len(s) == 2 else np.zeros(s, dtype=np.float32) for s in CONFIG1_SHAPES]
+
+
+def config1_grads():
+    """Generator of per-step gradient lists (float32 numpy), seed 0."""
+    rng = np.random.default_rng(0)
+    for _ in range(CONFIG1_STEPS):
+        yield [(rng.standard_normal(s) * 1e-3).astype(np.float32) for s in CONFIG1_SHAPES]

@@ -101,6 +101,27 @@ def run_case(optimi, case, device):
     return out
 
 
+def run_config1(optimi, device):
+    """BASELINE configuration 1 through the reference's foreach path; returns strided samples."""
+    from cases import CONFIG1_HYPER, CONFIG1_STRIDE, config1_grads, config1_params
+
+    params = [torch.from_numpy(p).to(device).requires_grad_(True) for p in config1_params()]
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        opt = optimi.AdamW(params, foreach=True, triton=False, **CONFIG1_HYPER)
+    for grads in config1_grads():
+        for p, g in zip(params, grads):
+            p.grad = torch.from_numpy(g).to(device)
+        opt.step()
+        opt.zero_grad()
+    out = {}
+    for i, p in enumerate(params):
+        out[f"{i}.param"] = to_bits(p.detach().reshape(-1)[::CONFIG1_STRIDE])
+        for name in ("exp_avg", "exp_avg_sq"):
+            out[f"{i}.{name}"] = to_bits(opt.state[p][name].reshape(-1)[::CONFIG1_STRIDE])
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="directory that contains the reference's `optimi` package")
@@ -122,6 +143,8 @@ def main():
         for k, v in res.items():
             blob[f"{case.name}/{k}"] = v
         n += 1
+    for k, v in run_config1(optimi, args.device).items():
+        blob[f"config1/{k}"] = v
     blob["__meta__"] = np.array(
         f"optimi {optimi.__version__}; torch {torch.__version__}; device {args.device}"
         + (f" ({torch.cuda.get_device_name(0)})" if args.device == "cuda" else "")

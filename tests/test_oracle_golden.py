@@ -41,3 +41,28 @@ def test_oracle_matches_reference_on_cpu_f32(case):
     rtol = 2e-6 if case.opt == "adan" else 1e-6
     for key, t in got.items():
         assert _rel_close(t, golden_tensor(CPU, case, key), rtol, 1e-9), key
+
+
+def _config1_oracle():
+    from cases import CONFIG1_HYPER, config1_grads, config1_params
+    from oracle.port import OracleOptimizer
+
+    params = [torch.from_numpy(p) for p in config1_params()]
+    opt = OracleOptimizer("adamw", params, **CONFIG1_HYPER)
+    for grads in config1_grads():
+        opt.step([torch.from_numpy(g) for g in grads])
+    return opt
+
+
+def test_oracle_config1_matches_reference_on_cpu():
+    """BASELINE configuration 1 (AdamW float32, 2-layer MLP parameter set, 20 steps) at full size; the
+    golden holds every 997th element of what the reference's CPU foreach path produced."""
+    from cases import CONFIG1_STRIDE
+
+    opt = _config1_oracle()
+    for i, p in enumerate(opt.params):
+        for name, t in (("param", p), ("exp_avg", opt.state[i]["exp_avg"]), ("exp_avg_sq", opt.state[i]["exp_avg_sq"])):
+            want = torch.from_numpy(CPU[f"config1/{i}.{name}"].copy())
+            # parameters that pass close to zero get an absolute floor of 1e-6 of the weights' scale (0.02 .. 0.1)
+            atol = 1e-7 if name == "param" else 1e-10
+            assert _rel_close(t.reshape(-1)[::CONFIG1_STRIDE], want, 1e-6, atol), f"tensor {i} {name}"

@@ -215,3 +215,32 @@ def test_functional_api_matches_classes(cname, fname, kw, keys):
             if k in ("eps_sq",) or states[k] is None:
                 continue
             assert torch.equal(opt.state[p][k], states[k][i]), f"{k} of tensor {i}"
+
+
+def test_config1_full_size():
+    """BASELINE configuration 1 at full size: kernels == oracle on every element (float32, bit for bit),
+    and == the reference's CUDA foreach result on the sampled elements of the golden (when the golden
+    file carries them)."""
+    import optimi_b200
+    from cases import CONFIG1_HYPER, CONFIG1_STRIDE, config1_grads, config1_params
+    from oracle.port import OracleOptimizer
+
+    host = [torch.from_numpy(p) for p in config1_params()]
+    oracle = OracleOptimizer("adamw", [h.clone() for h in host], **CONFIG1_HYPER)
+    params = [h.clone().cuda().requires_grad_(True) for h in host]
+    opt = optimi_b200.AdamW(params, **CONFIG1_HYPER)
+    for grads in config1_grads():
+        gs = [torch.from_numpy(g) for g in grads]
+        for p, g in zip(params, gs):
+            p.grad = g.cuda()
+        opt.step()
+        opt.zero_grad()
+        oracle.step(gs)
+    torch.cuda.synchronize()
+    for i, p in enumerate(params):
+        for name, got, want in (("param", p.detach(), oracle.params[i]), ("exp_avg", opt.state[p]["exp_avg"], oracle.state[i]["exp_avg"]),
+                                ("exp_avg_sq", opt.state[p]["exp_avg_sq"], oracle.state[i]["exp_avg_sq"])):  # fmt: skip
+            assert torch.equal(got.cpu(), want), f"tensor {i} {name} differs from the oracle"
+            key = f"config1/{i}.{name}"
+            if key in CUDA.files:
+                assert torch.equal(got.cpu().reshape(-1)[::CONFIG1_STRIDE], torch.from_numpy(CUDA[key].copy())), f"tensor {i} {name} differs from the reference"
