@@ -1,5 +1,8 @@
 """ZeRO-1 sharding on real GPUs (needs at least two): the sharded step + NCCL all-gather must leave
-every rank with exactly the parameters of an unsharded run."""
+every rank with exactly the parameters of an unsharded run.
+
+The tests run two ranks by default; ``OPTIMI_TEST_WORLD=4`` (or 8) on a machine with that many GPUs
+runs the same cases over more ranks (the gradient-mean kernels are compiled per rank bound 2, 4, 8)."""
 
 import os
 import socket
@@ -10,6 +13,13 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 pytestmark = pytest.mark.gpu
+
+
+def _world():
+    world = int(os.environ.get("OPTIMI_TEST_WORLD", "2"))
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    return world
 
 
 def _free_port():
@@ -66,9 +76,7 @@ def _worker(rank, world, port, cname, kw, exchange, out):
     ("Ranger", dict(lr=3e-4, k=2), "push"),
 ])  # fmt: skip
 def test_sharded_step_equals_unsharded(cname, kw, exchange):
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
-    world = 2
+    world = _world()
     ctx = mp.get_context("spawn")
     out = ctx.SimpleQueue()
     port = _free_port()
@@ -127,9 +135,7 @@ def _reduce_worker(rank, world, port, cname, kw, out):
                                       ("Adan", dict(lr=3e-4, kahan_sum=True))])  # fmt: skip
 def test_fused_gradient_mean_step_and_exchange(cname, kw):
     """reduce-scatter + step + all-gather in one kernel: equals an unsharded step on the mean gradient."""
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
-    world = 2
+    world = _world()
     ctx = mp.get_context("spawn")
     out = ctx.SimpleQueue()
     port = _free_port()
