@@ -44,6 +44,7 @@ extern "C" {
 #define OPTIMI_ERR_INVALID_ARGUMENT (-1)
 #define OPTIMI_ERR_CUDA (-2)
 #define OPTIMI_ERR_WORKSPACE_TOO_SMALL (-3)
+#define OPTIMI_ERR_CAPTURE (-4) /* a launch met a capturing stream outside a record bracket, or the reverse */
 
 const char* optimi_b200_last_error(void);
 
@@ -52,6 +53,39 @@ int optimi_b200_version(void);
 
 /* Number of CUDA kernels this library has launched in the calling process so far (all threads). */
 unsigned long long optimi_b200_launch_count(void);
+
+/* Steps inside a CUDA graph.  No counterpart in the reference (its kernels are launched eagerly
+ * from Python every step).
+ *
+ * Every kernel of this library takes its scalars by value, and most of them change from step to
+ * step (bias corrections, a scheduled learning rate, Ranger's lookahead flag), so a step that was
+ * merely captured would replay stale scalars.  A step entry point therefore refuses a capturing
+ * stream (OPTIMI_ERR_CAPTURE) unless the calling thread has opened a record bracket:
+ *
+ *   capture time   optimi_b200_graph_record_begin();
+ *                  ... the step calls, on the capturing stream: launches are captured as usual and
+ *                      the graph node of each is remembered ...
+ *                  optimi_b200_graph_record_end(&nodes);
+ *   every replay   optimi_b200_graph_update_begin(nodes, graph_exec);
+ *                  ... THE SAME step calls in the same order with the coming step's scalars (and
+ *                      pointers, which may differ): nothing is launched, each would-be launch
+ *                      rewrites the kernel parameters of its node in `graph_exec`
+ *                      (cudaGraphExecKernelNodeSetParams) ...
+ *                  optimi_b200_graph_update_end();      then launch the graph
+ *
+ * `graph_exec` is the cudaGraphExec_t instantiated from the captured graph; the captured
+ * cudaGraph_t must still exist while updates are made (its nodes name the ones to rewrite).  An
+ * update only affects launches of the graph made after it.  The brackets are per thread and do
+ * not nest; they have not been exercised together with the peer push / pull brackets below.  `nodes` is freed
+ * with optimi_b200_graph_nodes_free (NULL is fine).  update_end fails if the step issued a
+ * different number of launches than were recorded (the tensor list changed: capture again). */
+typedef struct optimi_b200_graph_nodes optimi_b200_graph_nodes;
+int optimi_b200_graph_record_begin(void);
+int optimi_b200_graph_record_end(optimi_b200_graph_nodes** out);
+int optimi_b200_graph_nodes_count(const optimi_b200_graph_nodes* nodes);
+void optimi_b200_graph_nodes_free(optimi_b200_graph_nodes* nodes);
+int optimi_b200_graph_update_begin(optimi_b200_graph_nodes* nodes, void* graph_exec);
+int optimi_b200_graph_update_end(void);
 
 /* Adam / AdamW.  Replaces _foreach_adam (optimi/adam.py:399-453), _single_param_adam
  * (optimi/adam.py:354-396) and the Triton launchers (optimi/adam.py:533-630); called where

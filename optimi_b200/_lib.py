@@ -35,7 +35,9 @@ SIGNATURES = {
     "optimi_b200_radam": [_I] + [_P] * 5 + [_P, _I] + [_D] * 6 + [_I, _D] + [_I] * 3 + [_P],
     "optimi_b200_ranger": [_I] + [_P] * 6 + [_P, _I] + [_D] * 6 + [_I, _D, _I, _D] + [_I] * 3 + [_P],
 }
-EXPORTS = list(SIGNATURES) + ["optimi_b200_push_begin", "optimi_b200_push_end", "optimi_b200_pull_begin", "optimi_b200_pull_end", "optimi_b200_last_error", "optimi_b200_version", "optimi_b200_launch_count", "optimi_b200_stableadamw_workspace_bytes"]
+EXPORTS = list(SIGNATURES) + ["optimi_b200_push_begin", "optimi_b200_push_end", "optimi_b200_pull_begin", "optimi_b200_pull_end", "optimi_b200_last_error", "optimi_b200_version", "optimi_b200_launch_count", "optimi_b200_stableadamw_workspace_bytes",
+                                   "optimi_b200_graph_record_begin", "optimi_b200_graph_record_end", "optimi_b200_graph_nodes_count",
+                                   "optimi_b200_graph_nodes_free", "optimi_b200_graph_update_begin", "optimi_b200_graph_update_end"]  # fmt: skip
 
 
 def _load() -> ctypes.CDLL:
@@ -63,6 +65,18 @@ def _load() -> ctypes.CDLL:
     lib.optimi_b200_launch_count.argtypes = []
     lib.optimi_b200_stableadamw_workspace_bytes.restype = ctypes.c_size_t
     lib.optimi_b200_stableadamw_workspace_bytes.argtypes = [_I, _P]
+    lib.optimi_b200_graph_record_begin.restype = _I
+    lib.optimi_b200_graph_record_begin.argtypes = []
+    lib.optimi_b200_graph_record_end.restype = _I
+    lib.optimi_b200_graph_record_end.argtypes = [ctypes.POINTER(ctypes.c_void_p)]
+    lib.optimi_b200_graph_nodes_count.restype = _I
+    lib.optimi_b200_graph_nodes_count.argtypes = [_P]
+    lib.optimi_b200_graph_nodes_free.restype = None
+    lib.optimi_b200_graph_nodes_free.argtypes = [_P]
+    lib.optimi_b200_graph_update_begin.restype = _I
+    lib.optimi_b200_graph_update_begin.argtypes = [_P, _P]
+    lib.optimi_b200_graph_update_end.restype = _I
+    lib.optimi_b200_graph_update_end.argtypes = []
     return lib
 
 
@@ -98,6 +112,57 @@ class peer_pull:
 
     def __exit__(self, *exc):
         LIB.optimi_b200_pull_end()
+
+
+class GraphNodes:
+    """The CUDA-graph nodes that the launches of one captured step became (an owned C handle)."""
+
+    def __init__(self, handle: int):
+        self.handle = handle
+
+    def __len__(self) -> int:
+        return LIB.optimi_b200_graph_nodes_count(self.handle)
+
+    def __del__(self):
+        if self.handle and LIB is not None:
+            LIB.optimi_b200_graph_nodes_free(self.handle)
+            self.handle = None
+
+
+class graph_record:
+    """Context manager for a step made on a capturing stream: this thread's launches are captured as
+    usual and their graph nodes remembered; `.nodes` holds them afterwards."""
+
+    nodes: GraphNodes | None = None
+
+    def __enter__(self):
+        check(LIB.optimi_b200_graph_record_begin())
+        return self
+
+    def __exit__(self, *exc):
+        out = ctypes.c_void_p()
+        rc = LIB.optimi_b200_graph_record_end(ctypes.byref(out))
+        if rc == 0:
+            self.nodes = GraphNodes(out.value)
+        if exc[0] is None:
+            check(rc)
+
+
+class graph_update:
+    """Context manager: the step calls made by this thread inside it launch nothing; each would-be
+    launch rewrites the kernel parameters of the corresponding recorded node in `graph_exec`."""
+
+    def __init__(self, nodes: GraphNodes, graph_exec: int):
+        self.nodes, self.graph_exec = nodes, graph_exec
+
+    def __enter__(self):
+        check(LIB.optimi_b200_graph_update_begin(self.nodes.handle, self.graph_exec))
+        return self
+
+    def __exit__(self, *exc):
+        rc = LIB.optimi_b200_graph_update_end()
+        if exc[0] is None:
+            check(rc)
 
 
 def check(rc: int) -> None:

@@ -10,6 +10,7 @@
 #include <cstring>
 #include <mutex>
 #include <type_traits>
+#include <vector>
 
 #include "optimizer_ops.cuh"
 
@@ -43,10 +44,87 @@ static int fail(int code, const char* fmt, ...) {
 
 OPTIMI_SHARED(std::atomic<unsigned long long> g_launches, {0});
 
-static int check_launch(const char* what) {
+// ---------------------------------------------------------------------------------------------
+// launches, and their life inside a CUDA graph
+// ---------------------------------------------------------------------------------------------
+// Every kernel receives its scalars by value, so a launch captured into a CUDA graph would repeat
+// the scalars of the step it was captured at (bias corrections, learning rate) on every replay.
+// Instead of a second family of kernels that read their scalars from device memory, the library
+// remembers which graph nodes its launches became (record mode) and later rewrites those nodes'
+// kernel parameters in the instantiated graph with the scalars of the coming step (update mode):
+// the caller repeats the very same step calls, and each would-be launch turns into one
+// cudaGraphExecKernelNodeSetParams.  Outside both modes a launch into a capturing stream is
+// refused, because it would silently freeze the step count.
+struct GraphNodes {
+  std::vector<cudaGraphNode_t> nodes;
+};
+enum GraphMode : int { kGraphNone = 0, kGraphRecord = 1, kGraphUpdate = 2 };
+struct GraphState {
+  int mode;
+  GraphNodes* nodes;      // record: being filled; update: being walked
+  size_t cursor;          // update: next node
+  cudaGraphExec_t exec;   // update: the instantiated graph
+};
+OPTIMI_SHARED(thread_local GraphState g_graph, = {kGraphNone COMMA nullptr COMMA 0 COMMA nullptr});
+
+template <class... P>
+static int launch_kernel(const char* what, void (*kernel)(P...), unsigned grid, unsigned block, cudaStream_t stream,
+                         const P&... params) {
+  void* kernel_params[] = {const_cast<void*>(static_cast<const void*>(&params))...};
+  if (g_graph.mode == kGraphUpdate) {
+    GraphNodes& gn = *g_graph.nodes;
+    if (g_graph.cursor >= gn.nodes.size())
+      return fail(OPTIMI_ERR_INVALID_ARGUMENT, "%s: this step issues more launches than were recorded (%zu); capture it again", what,
+                  gn.nodes.size());
+    cudaKernelNodeParams np;
+    memset(&np, 0, sizeof(np));
+    np.func = reinterpret_cast<void*>(kernel);
+    np.gridDim = dim3(grid);
+    np.blockDim = dim3(block);
+    np.sharedMemBytes = 0;
+    np.kernelParams = kernel_params;
+    np.extra = nullptr;
+    cudaError_t e = cudaGraphExecKernelNodeSetParams(g_graph.exec, gn.nodes[g_graph.cursor], &np);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      return fail(OPTIMI_ERR_CUDA, "%s: cudaGraphExecKernelNodeSetParams on recorded node %zu: %s", what, g_graph.cursor,
+                  cudaGetErrorString(e));
+    }
+    g_graph.cursor++;
+    return OPTIMI_OK;
+  }
+  cudaStreamCaptureStatus status = cudaStreamCaptureStatusNone;
+  cudaError_t e = cudaStreamIsCapturing(stream, &status);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(OPTIMI_ERR_CUDA, "%s: cudaStreamIsCapturing: %s", what, cudaGetErrorString(e));
+  }
+  if (g_graph.mode == kGraphNone && status != cudaStreamCaptureStatusNone)
+    return fail(OPTIMI_ERR_CAPTURE,
+                "%s: the stream is capturing a CUDA graph; a plain launch would repeat this step's scalars on every replay. "
+                "Bracket the step with optimi_b200_graph_record_begin/_end and refresh the graph with "
+                "optimi_b200_graph_update_begin/_end before each replay",
+                what);
+  if (g_graph.mode == kGraphRecord && status != cudaStreamCaptureStatusActive)
+    return fail(OPTIMI_ERR_CAPTURE, "%s: recording graph nodes, but the stream is not capturing", what);
+  e = cudaLaunchKernel(reinterpret_cast<const void*>(kernel), dim3(grid), dim3(block), kernel_params, 0, stream);
   g_launches.fetch_add(1, std::memory_order_relaxed);
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return fail(OPTIMI_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(OPTIMI_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+  }
+  if (g_graph.mode == kGraphRecord) {
+    // the node this launch became is the stream's only capture dependency now
+    const cudaGraphNode_t* deps = nullptr;
+    size_t n_deps = 0;
+    e = cudaStreamGetCaptureInfo(stream, &status, nullptr, nullptr, &deps, &n_deps);
+    if (e != cudaSuccess || status != cudaStreamCaptureStatusActive || n_deps != 1 || !deps) {
+      cudaGetLastError();
+      return fail(OPTIMI_ERR_CUDA, "%s: cannot identify the captured kernel node (%s, %zu dependencies)", what,
+                  cudaGetErrorString(e), n_deps);
+    }
+    g_graph.nodes->nodes.push_back(deps[0]);
+  }
   return OPTIMI_OK;
 }
 
@@ -131,13 +209,11 @@ static int launch_op(const char* name, int n, const int64_t* numels, void* const
                      const typename Op::Args& args, cudaStream_t stream) {
   if (n <= MtaTable<Op::NL, true>::CAP) {  // few tensors (a gradient-release step): the small table
     return for_each_table<Op::NL, true>(n, numels, lists, tile_of<T, Op>(), [&](const MtaTable<Op::NL, true>& tab, int tiles) {
-      mta_kernel<T, Op, true><<<tiles, kThreads, 0, stream>>>(tab, args);
-      return check_launch(name);
+      return launch_kernel(name, mta_kernel<T, Op, true>, tiles, kThreads, stream, tab, args);
     });
   }
   return for_each_table<Op::NL, false>(n, numels, lists, tile_of<T, Op>(), [&](const MtaTable<Op::NL, false>& tab, int tiles) {
-    mta_kernel<T, Op, false><<<tiles, kThreads, 0, stream>>>(tab, args);
-    return check_launch(name);
+    return launch_kernel(name, mta_kernel<T, Op, false>, tiles, kThreads, stream, tab, args);
   });
 }
 
@@ -308,11 +384,12 @@ static int stableadamw_typed(int n, void* const* params, void* const* grads, voi
   auto pass_a = [&](auto small) {
     constexpr bool SMALL = decltype(small)::value;
     return for_each_table<4, SMALL>(n, numels, lists_a, tile_a, [&](const MtaTable<4, SMALL>& tab, int tiles) {
-      stable_moments_sum_kernel<T, SMALL><<<tiles, kThreads, 0, stream>>>(tab, ma, partial);
-      int r = check_launch("optimi_b200_stableadamw (moments)");
+      int r = launch_kernel("optimi_b200_stableadamw (moments)", stable_moments_sum_kernel<T, SMALL>, tiles, kThreads, stream, tab,
+                            ma, partial);
       if (r != OPTIMI_OK) return r;
-      stable_finalize_kernel<T, SMALL><<<tab.n_tensors, 256, 0, stream>>>(tab, fa, partial, tensor_scalars);
-      return check_launch("optimi_b200_stableadamw (finalize)");
+      const double* partial_in = partial;
+      return launch_kernel("optimi_b200_stableadamw (finalize)", stable_finalize_kernel<T, SMALL>, tab.n_tensors, 256, stream,
+                           tab, fa, partial_in, tensor_scalars);
     });
   };
   int rc = n <= MtaTable<4, true>::CAP ? pass_a(std::true_type{}) : pass_a(std::false_type{});
@@ -375,6 +452,60 @@ int optimi_b200_pull_begin(int n_ranks, const int64_t* grad_deltas, double scale
 void optimi_b200_pull_end(void) { g_pull.n = 0; }
 
 unsigned long long optimi_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int optimi_b200_graph_record_begin(void) {
+  if (g_graph.mode != kGraphNone)
+    return fail(OPTIMI_ERR_INVALID_ARGUMENT, "optimi_b200_graph_record_begin: a record or update bracket is already open on this thread");
+  g_graph.mode = kGraphRecord;
+  g_graph.nodes = new GraphNodes();
+  g_graph.cursor = 0;
+  g_graph.exec = nullptr;
+  return OPTIMI_OK;
+}
+
+int optimi_b200_graph_record_end(optimi_b200_graph_nodes** out) {
+  if (g_graph.mode != kGraphRecord)
+    return fail(OPTIMI_ERR_INVALID_ARGUMENT, "optimi_b200_graph_record_end: no record bracket is open on this thread");
+  GraphNodes* nodes = g_graph.nodes;
+  g_graph = GraphState{kGraphNone, nullptr, 0, nullptr};
+  if (!out) {
+    delete nodes;
+    return fail(OPTIMI_ERR_INVALID_ARGUMENT, "optimi_b200_graph_record_end: out is NULL");
+  }
+  *out = reinterpret_cast<optimi_b200_graph_nodes*>(nodes);
+  return OPTIMI_OK;
+}
+
+int optimi_b200_graph_nodes_count(const optimi_b200_graph_nodes* nodes) {
+  return nodes ? (int)reinterpret_cast<const GraphNodes*>(nodes)->nodes.size() : 0;
+}
+
+void optimi_b200_graph_nodes_free(optimi_b200_graph_nodes* nodes) { delete reinterpret_cast<GraphNodes*>(nodes); }
+
+int optimi_b200_graph_update_begin(optimi_b200_graph_nodes* nodes, void* graph_exec) {
+  const char* fn = "optimi_b200_graph_update_begin";
+  if (g_graph.mode != kGraphNone) return fail(OPTIMI_ERR_INVALID_ARGUMENT, "%s: a record or update bracket is already open on this thread", fn);
+  if (!nodes) return fail(OPTIMI_ERR_INVALID_ARGUMENT, "%s: nodes is NULL", fn);
+  if (!graph_exec) return fail(OPTIMI_ERR_INVALID_ARGUMENT, "%s: graph_exec is NULL", fn);
+  g_graph.mode = kGraphUpdate;
+  g_graph.nodes = reinterpret_cast<GraphNodes*>(nodes);
+  g_graph.cursor = 0;
+  g_graph.exec = reinterpret_cast<cudaGraphExec_t>(graph_exec);
+  return OPTIMI_OK;
+}
+
+int optimi_b200_graph_update_end(void) {
+  if (g_graph.mode != kGraphUpdate)
+    return fail(OPTIMI_ERR_INVALID_ARGUMENT, "optimi_b200_graph_update_end: no update bracket is open on this thread");
+  const size_t visited = g_graph.cursor, recorded = g_graph.nodes->nodes.size();
+  g_graph = GraphState{kGraphNone, nullptr, 0, nullptr};
+  if (visited != recorded)
+    return fail(OPTIMI_ERR_INVALID_ARGUMENT,
+                "optimi_b200_graph_update_end: the step issued %zu launches but %zu were recorded; the rest of the graph still "
+                "holds the previous step's scalars — capture the step again",
+                visited, recorded);
+  return OPTIMI_OK;
+}
 
 int optimi_b200_adam(int n, void* const* params, void* const* grads, void* const* exp_avgs, void* const* exp_avg_sqs,
                      void* const* kahan_comps, const int64_t* numels, int dtype, double lr, double beta1_comp,

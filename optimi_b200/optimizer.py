@@ -190,6 +190,7 @@ class OptimiOptimizer(Optimizer):
         self.register_load_state_dict_post_hook(lambda opt: opt._drop_plans())
         self._release_stream: torch.cuda.Stream | None = None
         self._release_fence_queued = False
+        self._graph_nodes: _lib.GraphNodes | None = None  # kernel nodes of the step captured into a CUDA graph
 
         if self.defaults["gradient_release"]:
             if self.defaults["foreach"]:
@@ -262,14 +263,61 @@ class OptimiOptimizer(Optimizer):
                 loss = closure()
 
         if param is None:
-            for group in self.param_groups:
-                self._step_group(group)
+            if torch.cuda.is_initialized() and torch.cuda.is_current_stream_capturing():
+                self._capture_step()
+            else:
+                for group in self.param_groups:
+                    self._step_group(group)
         else:
             self._release(param)
         return loss
 
+    # ---- the step inside a CUDA graph -----------------------------------------------------------
+    def _capture_step(self) -> None:
+        """`step()` on a capturing stream: the launches go into the graph and the library remembers
+        which nodes they became.  Nothing runs and no step counter moves; `update_graph` gives the
+        nodes the scalars of each coming step."""
+        record = _lib.graph_record()
+        with record:
+            for group in self.param_groups:
+                self._step_group(group, capturing=True)
+        self._graph_nodes = record.nodes
+
+    def update_graph(self, graph: "torch.cuda.CUDAGraph") -> None:
+        """Prepares the next replay of a CUDA graph that holds a captured `step()`.
+
+        The kernels take the step's host scalars (bias corrections from the step count, the current
+        `lr` and the other hyper-parameters of each `param_group`, Ranger's lookahead flag) by value,
+        so a captured step has to be told about every new step: this advances the step counters as
+        `step()` would and rewrites the kernel parameters of the captured launches in the
+        instantiated graph, without launching anything.  Call it once before every
+        `graph.replay()`.  The graph must have been created with `keep_graph=True` and instantiated
+        (`torch.cuda.CUDAGraph(keep_graph=True)`, capture, `graph.instantiate()`): updating an
+        instantiated graph names its nodes through the captured graph, which PyTorch otherwise
+        discards.  Optimizer states must exist before the capture (run one eager step first) and
+        gradients have to live where they lived during capture or be re-pointed before this call,
+        which also passes the current gradient addresses on.
+
+            opt.step()                                   # eager: creates the states
+            g = torch.cuda.CUDAGraph(keep_graph=True)
+            with torch.cuda.graph(g):
+                opt.step()                               # captured, not run
+            g.instantiate()
+            for _ in range(steps):
+                ...fill the static gradients, change param_group["lr"]...
+                opt.update_graph(g)
+                g.replay()
+        """
+        if self._graph_nodes is None:
+            raise RuntimeError("update_graph: no captured step to update; call step() under torch.cuda.graph(...) first")
+        graph.raw_cuda_graph()  # raises unless the graph was created with keep_graph=True
+        graph_exec = graph.raw_cuda_graph_exec()
+        with torch.no_grad(), _lib.graph_update(self._graph_nodes, graph_exec):
+            for group in self.param_groups:
+                self._step_group(group)
+
     # ---- whole-list step of one parameter group ---------------------------------------------------
-    def _step_group(self, group: dict[str, Any]) -> None:
+    def _step_group(self, group: dict[str, Any], capturing: bool = False) -> None:
         """One step of every parameter of `group` that has a gradient: one C call per (device, dtype).
 
         The pointer tables of parameters and states are cached (`_GroupPlan`) for as long as the same
@@ -281,13 +329,21 @@ class OptimiOptimizer(Optimizer):
         key = tuple(map(id, params))
         plan = self._group_plans.get(id(group))
         if plan is None or plan.key != key or not plan.fresh():
+            if capturing and (not group["setup"] or any("kahan_comp" not in self.state[p] for p in params)):
+                raise RuntimeError(
+                    "step() under CUDA graph capture needs the optimizer states to exist already (their allocation and "
+                    "zero-fill would become part of the graph): run one eager step() before capturing"
+                )
             for p in params:
                 self._init_state(group, self.state[p], p)
             self._setup_group(group)
             plan = self._group_plans[id(group)] = _GroupPlan(self, group, params, key) if params else None
         t = 0
         if self._counts_steps:
-            t = F._advance(group["step"])  # the reference advances the counter even when no parameter has a gradient
+            if capturing:  # nothing runs during capture: the counter moves in update_graph
+                t = int(group["step"].item()) + 1
+            else:
+                t = F._advance(group["step"])  # the reference advances the counter even when no parameter has a gradient
         if plan is None:
             return
         tail = type(self)._tail(t, True, kahan_sum=group["kahan_sum"], **{k: group[k] for k in self._scalar_keys})

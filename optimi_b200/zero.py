@@ -300,6 +300,8 @@ class ShardedOptimizer:
 
     @torch.no_grad()
     def step(self, shard_grads: list[Tensor] | None = None):
+        if torch.cuda.is_initialized() and torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("ShardedOptimizer.step() cannot be captured into a CUDA graph")
         self.step_local(shard_grads)
         self.gather_params()
 

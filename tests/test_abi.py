@@ -76,3 +76,20 @@ def test_cpu_tensors_are_refused_loudly():
     opt = optimi_b200.Lion([p], lr=1e-4)
     with pytest.raises(RuntimeError, match="CUDA tensors only"):
         opt.step()
+
+
+def test_graph_brackets_reject_misuse_without_touching_the_device():
+    from optimi_b200 import _lib
+
+    L = _lib.LIB
+    assert L.optimi_b200_graph_record_end(None) == -1 and b"no record bracket" in L.optimi_b200_last_error()
+    assert L.optimi_b200_graph_update_end() == -1 and b"no update bracket" in L.optimi_b200_last_error()
+    assert L.optimi_b200_graph_update_begin(None, None) == -1 and b"nodes is NULL" in L.optimi_b200_last_error()
+    assert L.optimi_b200_graph_record_begin() == 0
+    assert L.optimi_b200_graph_record_begin() == -1 and b"already open" in L.optimi_b200_last_error()
+    out = ctypes.c_void_p()
+    assert L.optimi_b200_graph_record_end(ctypes.byref(out)) == 0 and out.value
+    assert L.optimi_b200_graph_nodes_count(out) == 0  # a step with no launches
+    assert L.optimi_b200_graph_update_begin(out, None) == -1 and b"graph_exec is NULL" in L.optimi_b200_last_error()
+    L.optimi_b200_graph_nodes_free(out)
+    L.optimi_b200_graph_nodes_free(None)
