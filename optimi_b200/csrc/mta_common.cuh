@@ -275,6 +275,8 @@ __device__ __forceinline__ float pull_one(const PeerPull& pull, const T* local) 
 //   elem<T>(e, args, ctx)     the arithmetic for ONE element; e[l] is the element of list l as fp32
 //   kSumSlot                  index of an e[] slot whose values compute_vec sums up (-1: none)
 //   kMinBlocks                blocks that must fit on one SM (register cap for the compiler)
+//   kWholeTileBranch          give whole tiles their own straight-line branch (a code-generation choice
+//                             made per op by measurement: +8 % for Lion and StableAdamW, -7 % for Adam)
 //   kPush                     also store updated parameters into the peers' copies (Args has .push)
 //   kPull                     0, or the rank bound (2/4/8) of a launch whose gradients are the scaled sum of all
 //                             ranks' gradient buffers (Args has .pull)
@@ -366,8 +368,21 @@ __device__ __forceinline__ double process_tile(const Table& tab, const typename 
   const typename Op::Ctx ctx = Op::context(tab, s, args);
   double acc = 0.0;
   int done = 0;
+  if (Op::kWholeTileBranch && kTilesPerBlock == 1 && aligned && s.len == TILE) {
+    // a whole tile, as straight-line code ahead of the general loops below (same work; for some ops
+    // the compiler's schedule of this form runs measurably faster, for others slower: see kWholeTileBranch)
+    Vecs<Op::NL> v[U];
+#pragma unroll
+    for (int u = 0; u < U; u++) load_vec<T, Op>(v[u], p, (u * kThreads + threadIdx.x) * V, args);
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      const float part = compute_vec<T, Op>(v[u], args, ctx);
+      store_vec<T, Op>(v[u], p, (u * kThreads + threadIdx.x) * V, args);
+      if (Op::kSumSlot >= 0) acc += (double)part;
+    }
+    return acc;
+  }
   if (aligned) {
-    // full tiles: every load of the tile issued up front, then compute and store
     for (; done + TILE <= s.len; done += TILE) {
       Vecs<Op::NL> v[U];
 #pragma unroll
@@ -399,7 +414,8 @@ __device__ __forceinline__ double process_tile(const Table& tab, const typename 
 // fp16 needs the IEEE square root and a two-instruction rounding, hence a slightly larger budget.
 template <typename T, class Op>
 constexpr int min_blocks() {
-  return sizeof(T) == 2 && !__is_same(T, __nv_bfloat16) ? (Op::kMinBlocks > 2 ? Op::kMinBlocks - 2 : 1) : Op::kMinBlocks;
+  constexpr int capped = Op::kMinBlocks > 10 ? 10 : Op::kMinBlocks;
+  return sizeof(T) == 2 && !__is_same(T, __nv_bfloat16) ? (capped > 2 ? capped - 2 : 1) : Op::kMinBlocks;
 }
 
 template <typename T, class Op, bool SMALL>

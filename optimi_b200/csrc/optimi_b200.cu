@@ -279,7 +279,7 @@ static int dispatch(const char* name, int dtype, bool kahan, bool update, int n,
 // g^2 / max(v, eps^2) to partial[tile] — one double per tile, written (not accumulated), so the
 // scratch needs no clearing and the result does not depend on block scheduling.
 template <typename T, bool SMALL>
-__global__ void __launch_bounds__(kThreads, 10) stable_moments_sum_kernel(const __grid_constant__ MtaTable<4, SMALL> tab,
+__global__ void __launch_bounds__(kThreads, kStableMinBlocks) stable_moments_sum_kernel(const __grid_constant__ MtaTable<4, SMALL> tab,
                                                                       const __grid_constant__ StableMomentsArgs a,
                                                                       double* __restrict__ partial) {
   Span s;

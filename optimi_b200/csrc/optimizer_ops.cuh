@@ -71,6 +71,7 @@ struct OpBase {
   static constexpr int kMinBlocks = OPTIMI_MIN_BLOCKS;  // 10: <= 51 registers per thread at 128 threads
   static constexpr bool kPush = false;
   static constexpr int kPull = 0;
+  static constexpr bool kWholeTileBranch = false;
   template <class Table, class Args>
   static __device__ __forceinline__ NoCtx context(const Table&, const Span&, const Args&) { return NoCtx{}; }
 };
@@ -131,6 +132,7 @@ struct PeerOp {
                                                 : (Base::kMinBlocks > 5 ? Base::kMinBlocks - 5 : 1);
   static constexpr bool kPush = true;
   static constexpr int kPull = PULL;
+  static constexpr bool kWholeTileBranch = false;
   using Args = PeerArgs<typename Base::Args>;
   using Ctx = typename Base::Ctx;
   template <class Table>
@@ -157,7 +159,9 @@ struct RangerArgs {
 template <bool KAHAN, bool UPDATE, bool LOOK>
 struct RangerOp : OpBase {
   static constexpr int NL = 6, U = OPTIMI_U_ADAM;
-  static constexpr int kMinBlocks = LOOK ? 8 : OPTIMI_MIN_BLOCKS;  // six streams: <= 64 registers; five: as Adam
+  // six streams: <= 64 registers; five: as Adam (RAdam then spills one register, which measured 1 % faster
+  // than nine blocks without the spill)
+  static constexpr int kMinBlocks = LOOK ? 8 : OPTIMI_MIN_BLOCKS;
   using Args = RangerArgs;
   static __device__ __forceinline__ bool reads(int l, const Args&) {
     return l == 0 ? UPDATE : l == 4 ? KAHAN : l == 5 ? (UPDATE && LOOK) : true;
@@ -209,6 +213,7 @@ struct LionArgs {
 template <bool KAHAN, bool UPDATE>
 struct LionOp : OpBase {
   static constexpr int NL = 4, U = OPTIMI_U_NARROW;
+  static constexpr bool kWholeTileBranch = true;
   using Args = LionArgs;
   static __device__ __forceinline__ bool reads(int l, const Args&) { return l == 0 ? UPDATE : l == 3 ? KAHAN : true; }
   static __device__ __forceinline__ bool writes(int l, const Args& a) { return l != 1 && reads(l, a); }
@@ -290,7 +295,7 @@ struct AdanArgs {
 template <bool KAHAN, bool UPDATE>
 struct AdanOp : OpBase {
   static constexpr int NL = 7, U = OPTIMI_U_WIDE;
-  static constexpr int kMinBlocks = 7;  // seven streams: <= 73 registers
+  static constexpr int kMinBlocks = 8;  // seven streams: 64 registers, the most that still compiles without spills
   using Args = AdanArgs;
   static __device__ __forceinline__ bool reads(int l, const Args&) { return l == 0 ? UPDATE : l == 6 ? KAHAN : true; }
   static __device__ __forceinline__ bool writes(int l, const Args& a) { return l != 1 && reads(l, a); }
@@ -330,9 +335,13 @@ struct StableMomentsArgs {
   float beta2_hat, beta2_comp, eps_sq;  // eps_sq: eps^2 rounded to the storage type
 };
 
+constexpr int kStableMinBlocks = 12;  // both StableAdamW passes fit 40 registers: twelve blocks per SM
+
 template <bool REDUCE>
 struct StableMomentsOp : OpBase {
   static constexpr int NL = 4, U = OPTIMI_U_NARROW;
+  static constexpr int kMinBlocks = kStableMinBlocks;
+  static constexpr bool kWholeTileBranch = true;
   static constexpr int kSumSlot = REDUCE ? 3 : -1;
   using Args = StableMomentsArgs;
   static __device__ __forceinline__ bool reads(int l, const Args&) { return l != 3; }
@@ -342,12 +351,13 @@ struct StableMomentsOp : OpBase {
     float &g = e[0], &m = e[1], &v = e[2];
     adam_moments<T>(m, v, g, a.l1, a.beta2_hat, a.beta2_comp);
     if (REDUCE) {
-      const float x = rnd<T>(fmaxf(v, a.eps_sq));
+      const float x = fmaxf(v, a.eps_sq);  // the larger of two values of the storage type: no rounding needed
       const float gg = rnd<T>(__fmul_rn(g, g));
-      // full-range approximate division (2 ulp): these terms only feed the per-tensor mean, whose
-      // summation order already differs from the reference's, and this pass is issue-bound
+      // approximate division (2 ulp for a divisor within 2^-126..2^126, which max(v, eps^2) is unless
+      // eps itself is absurd): these terms only feed the per-tensor mean, whose summation order
+      // already differs from the reference's, and this pass is issue-bound
       float q;
-      asm("div.full.f32 %0, %1, %2;" : "=f"(q) : "f"(gg), "f"(x));
+      asm("div.approx.f32 %0, %1, %2;" : "=f"(q) : "f"(gg), "f"(x));
       e[3] = rnd<T>(q);
     }
   }
@@ -367,9 +377,10 @@ template <bool KAHAN>
 struct StableUpdateOp {
   static constexpr int NL = 4, U = OPTIMI_U_NARROW;
   static constexpr int kSumSlot = -1;
-  static constexpr int kMinBlocks = 10;
+  static constexpr int kMinBlocks = kStableMinBlocks;
   static constexpr bool kPush = false;
   static constexpr int kPull = 0;
+  static constexpr bool kWholeTileBranch = true;
   using Args = StableUpdateArgs;
   using Ctx = float2;
   template <class Table>
