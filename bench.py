@@ -38,10 +38,10 @@ METRIC = "AdamW bf16-Kahan step: Gparams/s & HBM GB/s vs 8 TB/s, 8B shapes, 1/2/
 UNIT = "Gparams/s"
 BYTES_PER_PARAM = 18  # read p,g,m,v,k (10 B) + write p,m,v,k (8 B), bf16 + Kahan
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum per parameter of the AdamW bf16+Kahan kernel, from the ncu capture
-# of the 336 M-parameter case summarised in profiles/adamw_bf16_kahan_llama-0.3b_ncu_full.md; traffic is
-# proportional to the parameter count, so a launch's traffic is this figure times its elements
-NCU_DRAM_BYTES_PER_PARAM = 17.83
+# dram__bytes_read.sum + dram__bytes_write.sum per parameter of the bf16+Kahan kernels, from the ncu captures of the
+# 336 M-parameter case summarised in profiles/*_llama-0.3b_ncu_full.md (StableAdamW: both passes together); traffic is
+# proportional to the parameter count, so a step's traffic is this figure times its elements
+NCU_DRAM_BYTES_PER_PARAM = {"adamw": 17.83, "adam": 17.83, "lion": 13.83, "adan": 25.83, "stableadamw": 21.72}
 
 HYPER = dict(lr=3e-4, betas=(0.9, 0.99), weight_decay=1e-5, eps=1e-6, decouple_lr=True)
 
@@ -427,10 +427,12 @@ def run_b200_arm(args):
         peak, peak_kind = FALLBACK_HBM_GBS, "fallback"
     kernel_launches_per_step = max(1, launches // args.steps)
     achieved = bytes_per_param * n_local / (step_ms_max * 1e-3) / 1e9
-    traffic = NCU_DRAM_BYTES_PER_PARAM * n_local / kernel_launches_per_step if args.optimizer == "adamw" else None
+    ncu_bpp = NCU_DRAM_BYTES_PER_PARAM.get(args.optimizer)
+    traffic = ncu_bpp * n_local / kernel_launches_per_step if ncu_bpp is not None else None
     roofline = {
         "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": traffic,
-        "traffic_note": "bytes per launch: ncu dram read+write of a 336 M-param capture (17.83 B/param) scaled by elements per launch",
+        "traffic_note": (f"bytes per launch: ncu dram read+write of a 336 M-param capture ({ncu_bpp} B/param per step) scaled by "
+                         "elements per launch" if ncu_bpp is not None else "no ncu capture of this kernel"),
         "peak_kind": f"of {peak_kind}", "frac_of_8TBs": achieved / 8000.0, "kernel": kernel_name,
         "algorithmic_bytes_per_launch": bytes_per_param * n_local / kernel_launches_per_step,
         "algorithmic_bytes_per_param": bytes_per_param,
