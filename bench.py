@@ -52,7 +52,7 @@ OPTIMIZERS = {
     "adam": ("Adam", dict(lr=3e-4, betas=(0.9, 0.99), eps=1e-6), 18, "mta_kernel<bf16, AdamOp<kahan,update>>"),
     "lion": ("Lion", dict(lr=1e-4, betas=(0.9, 0.99)), 14, "mta_kernel<bf16, LionOp<kahan,update>>"),
     "sgd": ("SGD", dict(lr=1e-2, momentum=0.9), 14, "mta_kernel<bf16, SgdOp<kahan,update>>"),
-    "stableadamw": ("StableAdamW", dict(lr=3e-4), 22, "stable_moments_sum_kernel + mta_kernel<bf16, StableUpdateOp<kahan>>"),
+    "stableadamw": ("StableAdamW", dict(lr=3e-4), 22, "tile_sum_kernel<bf16, StableMomentsOp> + mta_kernel<bf16, StableUpdateOp<kahan>>"),
     "adan": ("Adan", dict(lr=3e-4, betas=(0.98, 0.92, 0.99), kahan_sum=True), 26, "mta_kernel<bf16, AdanOp<kahan,update>>"),
     "radam": ("RAdam", dict(lr=3e-4), 18, "mta_kernel<bf16, RangerOp<kahan,update>>"),
     # Lookahead (k=6) reads and writes the slow weights on every 6th step: 18 + 4/6 bytes on average

@@ -87,6 +87,31 @@ void optimi_b200_graph_nodes_free(optimi_b200_graph_nodes* nodes);
 int optimi_b200_graph_update_begin(optimi_b200_graph_nodes* nodes, void* graph_exec);
 int optimi_b200_graph_update_end(void);
 
+/* Gradient scaling fused into the step.  No counterpart in the reference: its users clip the gradient
+ * norm (torch.nn.utils.clip_grad_norm_) or unscale a loss scale (GradScaler.unscale_) in passes of
+ * their own between backward and step(), each a full read and write of the gradients.
+ *
+ * optimi_b200_grad_scale_begin(factor): until _end, every launch the calling thread makes through
+ * a step entry point multiplies each gradient element by the fp32 value at the DEVICE address
+ * `factor` as it is loaded, g <- round_to_storage(g * factor) — the arithmetic of
+ * torch._foreach_mul_(grads, factor_tensor) — and steps with that.  The gradient buffers are not
+ * written.  The value is read when the kernels run, so it may be produced on the same stream just
+ * before (optimi_b200_grad_clip_factor below, or a GradScaler's inverse scale).  Not combinable
+ * with the peer push / pull brackets.
+ *
+ * optimi_b200_grad_clip_factor: writes out[0] = min(1, max_norm * (1 / (total + 1e-6))) and
+ * out[1] = total, the 2-norm of all gradients, to the DEVICE array `out` (2 floats), following
+ * clip_grad_norm_'s own order of operations and roundings (per-tensor norms in the storage type,
+ * their 2-norm, reciprocal, product, clamp).  One read of the gradients; sums are taken in double
+ * in a fixed order, so the result is deterministic and agrees with PyTorch's up to the rounding of
+ * its fp32 sums (at most one unit of the storage type in the factor).  `workspace`: DEVICE scratch of
+ * optimi_b200_grad_clip_workspace_bytes(n_tensors, numels) bytes, 16-byte aligned. */
+void optimi_b200_grad_scale_begin(const float* device_factor);
+void optimi_b200_grad_scale_end(void);
+size_t optimi_b200_grad_clip_workspace_bytes(int n_tensors, const int64_t* numels);
+int optimi_b200_grad_clip_factor(int n_tensors, void* const* grads, const int64_t* numels, int dtype, double max_norm,
+                                 float* out, void* workspace, size_t workspace_bytes, void* stream);
+
 /* Adam / AdamW.  Replaces _foreach_adam (optimi/adam.py:399-453), _single_param_adam
  * (optimi/adam.py:354-396) and the Triton launchers (optimi/adam.py:533-630); called where
  * adam() picks its back end (optimi/adam.py:278-309).  `weight_decay` is the factor adam()

@@ -37,7 +37,9 @@ SIGNATURES = {
 }
 EXPORTS = list(SIGNATURES) + ["optimi_b200_push_begin", "optimi_b200_push_end", "optimi_b200_pull_begin", "optimi_b200_pull_end", "optimi_b200_last_error", "optimi_b200_version", "optimi_b200_launch_count", "optimi_b200_stableadamw_workspace_bytes",
                                    "optimi_b200_graph_record_begin", "optimi_b200_graph_record_end", "optimi_b200_graph_nodes_count",
-                                   "optimi_b200_graph_nodes_free", "optimi_b200_graph_update_begin", "optimi_b200_graph_update_end"]  # fmt: skip
+                                   "optimi_b200_graph_nodes_free", "optimi_b200_graph_update_begin", "optimi_b200_graph_update_end",
+                                   "optimi_b200_grad_scale_begin", "optimi_b200_grad_scale_end", "optimi_b200_grad_clip_workspace_bytes",
+                                   "optimi_b200_grad_clip_factor"]  # fmt: skip
 
 
 def _load() -> ctypes.CDLL:
@@ -65,6 +67,14 @@ def _load() -> ctypes.CDLL:
     lib.optimi_b200_launch_count.argtypes = []
     lib.optimi_b200_stableadamw_workspace_bytes.restype = ctypes.c_size_t
     lib.optimi_b200_stableadamw_workspace_bytes.argtypes = [_I, _P]
+    lib.optimi_b200_grad_scale_begin.restype = None
+    lib.optimi_b200_grad_scale_begin.argtypes = [_P]
+    lib.optimi_b200_grad_scale_end.restype = None
+    lib.optimi_b200_grad_scale_end.argtypes = []
+    lib.optimi_b200_grad_clip_workspace_bytes.restype = ctypes.c_size_t
+    lib.optimi_b200_grad_clip_workspace_bytes.argtypes = [_I, _P]
+    lib.optimi_b200_grad_clip_factor.restype = _I
+    lib.optimi_b200_grad_clip_factor.argtypes = [_I, _P, _P, _I, _D, _P, _P, ctypes.c_size_t, _P]
     lib.optimi_b200_graph_record_begin.restype = _I
     lib.optimi_b200_graph_record_begin.argtypes = []
     lib.optimi_b200_graph_record_end.restype = _I
@@ -112,6 +122,23 @@ class peer_pull:
 
     def __exit__(self, *exc):
         LIB.optimi_b200_pull_end()
+
+
+class grad_scale:
+    """Context manager: step launches made by this thread inside it multiply every gradient element by the
+    fp32 value stored at `factor` (a CUDA float32 tensor with one element) as they load it."""
+
+    def __init__(self, factor: torch.Tensor):
+        if factor.dtype != torch.float32 or not factor.is_cuda or factor.numel() < 1:
+            raise ValueError("the gradient factor must be a CUDA float32 tensor")
+        self.factor = factor
+
+    def __enter__(self):
+        LIB.optimi_b200_grad_scale_begin(self.factor.data_ptr())
+        return self
+
+    def __exit__(self, *exc):
+        LIB.optimi_b200_grad_scale_end()
 
 
 class GraphNodes:

@@ -217,6 +217,22 @@ static int launch_op(const char* name, int n, const int64_t* numels, void* const
   });
 }
 
+// Gradient factor requested for the calling thread's next launches (optimi_b200_grad_scale_begin / _end).
+OPTIMI_SHARED(thread_local const float* g_grad_factor, = nullptr);
+
+// Launches Op, or ScaledOp<Op> when a gradient factor is active.
+template <typename T, class Op>
+static int launch_maybe_scaled(const char* name, int n, const int64_t* numels, void* const* const (&lists)[Op::NL],
+                               const typename Op::Args& args, cudaStream_t stream) {
+  if (g_grad_factor) {
+    ScaledArgs<typename Op::Args> sa;
+    sa.base = args;
+    sa.factor = g_grad_factor;
+    return launch_op<T, ScaledOp<Op>>(name, n, numels, lists, sa, stream);
+  }
+  return launch_op<T, Op>(name, n, numels, lists, args, stream);
+}
+
 // Peer push / pull requested for the calling thread's next launches (optimi_b200_push_begin,
 // optimi_b200_pull_begin and their _end).
 OPTIMI_SHARED(thread_local PeerPush g_push, = {0 COMMA {0}});
@@ -227,6 +243,8 @@ OPTIMI_SHARED(thread_local PeerPull g_pull, = {0 COMMA 1.0f COMMA {0}});
 template <typename T, class Op, bool PULLABLE = true>
 static int launch_maybe_push(const char* name, int n, const int64_t* numels, void* const* const (&lists)[Op::NL],
                              const typename Op::Args& args, cudaStream_t stream) {
+  if (g_grad_factor && (g_pull.n > 0 || g_push.n > 0))
+    return fail(OPTIMI_ERR_INVALID_ARGUMENT, "%s: a gradient factor cannot be combined with the peer push / pull", name);
   if (g_pull.n > 0) {
     if constexpr (PULLABLE) {
       PeerArgs<typename Op::Args> pa;
@@ -247,7 +265,11 @@ static int launch_maybe_push(const char* name, int n, const int64_t* numels, voi
     pa.pull.n = 0;
     return launch_op<T, PeerOp<Op, 0>>(name, n, numels, lists, pa, stream);
   }
-  return launch_op<T, Op>(name, n, numels, lists, args, stream);
+  if constexpr (PULLABLE) {  // the ops with a gradient list
+    return launch_maybe_scaled<T, Op>(name, n, numels, lists, args, stream);
+  } else {
+    return launch_op<T, Op>(name, n, numels, lists, args, stream);
+  }
 }
 
 // Picks the instantiation for (dtype, kahan, update).  Kahan compensation exists only for the
@@ -257,13 +279,13 @@ static int dispatch(const char* name, int dtype, bool kahan, bool update, int n,
                     const Args& args, cudaStream_t stream) {
 #define OPTIMI_GO(T)                                                                                   \
   do {                                                                                                 \
-    if (!update) return launch_op<T, Op<false, false>>(name, n, numels, lists, args, stream);          \
+    if (!update) return launch_maybe_scaled<T, Op<false, false>>(name, n, numels, lists, args, stream); \
     if (kahan) return launch_maybe_push<T, Op<true, true>>(name, n, numels, lists, args, stream);      \
     return launch_maybe_push<T, Op<false, true>>(name, n, numels, lists, args, stream);                \
   } while (0)
   switch (dtype) {
     case OPTIMI_F32:
-      if (!update) return launch_op<float, Op<false, false>>(name, n, numels, lists, args, stream);
+      if (!update) return launch_maybe_scaled<float, Op<false, false>>(name, n, numels, lists, args, stream);
       return launch_maybe_push<float, Op<false, true>>(name, n, numels, lists, args, stream);
     case OPTIMI_BF16: OPTIMI_GO(__nv_bfloat16);
     case OPTIMI_F16: OPTIMI_GO(__half);
@@ -278,12 +300,13 @@ static int dispatch(const char* name, int dtype, bool kahan, bool update, int n,
 // Pass A with the per-tile sum: advances both averages and writes the tile's sum of
 // g^2 / max(v, eps^2) to partial[tile] — one double per tile, written (not accumulated), so the
 // scratch needs no clearing and the result does not depend on block scheduling.
-template <typename T, bool SMALL>
-__global__ void __launch_bounds__(kThreads, kStableMinBlocks) stable_moments_sum_kernel(const __grid_constant__ MtaTable<4, SMALL> tab,
-                                                                      const __grid_constant__ StableMomentsArgs a,
-                                                                      double* __restrict__ partial) {
+// Op = StableMomentsOp<true> (or its ScaledOp) for StableAdamW, SumSqOp for the gradient norm.
+template <typename T, class Op, bool SMALL>
+__global__ void __launch_bounds__(kThreads, kStableMinBlocks) tile_sum_kernel(const __grid_constant__ MtaTable<Op::NL, SMALL> tab,
+                                                                             const __grid_constant__ typename Op::Args a,
+                                                                             double* __restrict__ partial) {
   Span s;
-  double acc = process_tile<T, StableMomentsOp<true>>(tab, a, s);
+  double acc = process_tile<T, Op>(tab, a, s);
   __shared__ double warp_sum[kThreads / 32];
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, o);
@@ -335,6 +358,54 @@ __global__ void __launch_bounds__(256) stable_finalize_kernel(const __grid_const
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Gradient-norm clip factor: what torch.nn.utils.clip_grad_norm_ computes before it scales the
+// gradients (torch/nn/utils/clip_grad.py): per-tensor 2-norms in the storage type, the 2-norm of
+// those, and min(1, max_norm * (1 / (total + 1e-6))) with every intermediate rounded to the storage
+// type.  Pass 1 is tile_sum_kernel<T, SumSqOp>; these two finish the job.
+// ---------------------------------------------------------------------------------------------
+template <typename T, bool SMALL>
+__global__ void __launch_bounds__(256) norm_finalize_kernel(const __grid_constant__ MtaTable<2, SMALL> tab,
+                                                            const double* __restrict__ partial, float* __restrict__ tensor_norms) {
+  const int t = blockIdx.x;
+  const int c0 = tab.tile_start[t], c1 = tab.tile_start[t + 1];
+  double acc = 0.0;
+  for (int c = c0 + threadIdx.x; c < c1; c += 256) acc += partial[tab.tile_base + c];
+  __shared__ double warp_sum[8];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, o);
+  if ((threadIdx.x & 31) == 0) warp_sum[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double sum = 0.0;
+    for (int w = 0; w < 8; w++) sum += warp_sum[w];
+    tensor_norms[tab.tensor_base + t] = rnd<T>(__fsqrt_rn((float)sum));
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) clip_factor_kernel(const float* __restrict__ tensor_norms, int n_tensors, float max_norm,
+                                                          float* __restrict__ out) {
+  double acc = 0.0;
+  for (int i = threadIdx.x; i < n_tensors; i += 256) acc += (double)tensor_norms[i] * (double)tensor_norms[i];
+  __shared__ double warp_sum[8];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, o);
+  if ((threadIdx.x & 31) == 0) warp_sum[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double sum = 0.0;
+    for (int w = 0; w < 8; w++) sum += warp_sum[w];
+    const float total = rnd<T>(__fsqrt_rn((float)sum));
+    const float denom = rnd<T>(__fadd_rn(total, 1e-6f));
+    const float recip = rnd<T>(__fdiv_rn(1.0f, denom));
+    float factor = rnd<T>(__fmul_rn(recip, max_norm));
+    if (factor > 1.0f) factor = 1.0f;  // a NaN stays a NaN, as with torch.clamp
+    out[0] = factor;
+    out[1] = total;
+  }
+}
+
 static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 static long long count_tiles(int n, const int64_t* numels, int tile) {
@@ -362,7 +433,7 @@ static int stableadamw_typed(int n, void* const* params, void* const* grads, voi
   ma.eps_sq = round_to_storage<T>(eps * eps);
 
   void* const* const lists_a[4] = {grads, exp_avgs, exp_avg_sqs, nullptr};
-  if (!update) return launch_op<T, StableMomentsOp<false>>("optimi_b200_stableadamw (moments)", n, numels, lists_a, ma, stream);
+  if (!update) return launch_maybe_scaled<T, StableMomentsOp<false>>("optimi_b200_stableadamw (moments)", n, numels, lists_a, ma, stream);
 
   constexpr int tile_a = tile_of<T, StableMomentsOp<true>>();
   const size_t scal_bytes = align_up((size_t)n * sizeof(float2), 16);
@@ -384,8 +455,17 @@ static int stableadamw_typed(int n, void* const* params, void* const* grads, voi
   auto pass_a = [&](auto small) {
     constexpr bool SMALL = decltype(small)::value;
     return for_each_table<4, SMALL>(n, numels, lists_a, tile_a, [&](const MtaTable<4, SMALL>& tab, int tiles) {
-      int r = launch_kernel("optimi_b200_stableadamw (moments)", stable_moments_sum_kernel<T, SMALL>, tiles, kThreads, stream, tab,
-                            ma, partial);
+      int r;
+      if (g_grad_factor) {
+        ScaledArgs<StableMomentsArgs> sa;
+        sa.base = ma;
+        sa.factor = g_grad_factor;
+        r = launch_kernel("optimi_b200_stableadamw (moments)", tile_sum_kernel<T, ScaledOp<StableMomentsOp<true>>, SMALL>, tiles,
+                          kThreads, stream, tab, sa, partial);
+      } else {
+        r = launch_kernel("optimi_b200_stableadamw (moments)", tile_sum_kernel<T, StableMomentsOp<true>, SMALL>, tiles, kThreads,
+                          stream, tab, ma, partial);
+      }
       if (r != OPTIMI_OK) return r;
       const double* partial_in = partial;
       return launch_kernel("optimi_b200_stableadamw (finalize)", stable_finalize_kernel<T, SMALL>, tab.n_tensors, 256, stream,
@@ -685,6 +765,62 @@ int optimi_b200_stableadamw(int n, void* const* params, void* const* grads, void
       return stableadamw_typed<__half>(n, params, grads, exp_avgs, exp_avg_sqs, kahan_comps, numels, lr, beta1_comp, beta2_hat,
                                        beta2_comp, weight_decay, eps, decouple_lr, max_lr, kahan, update, workspace,
                                        workspace_bytes, s);
+  }
+}
+
+size_t optimi_b200_grad_clip_workspace_bytes(int n, const int64_t* numels) {
+  if (n <= 0 || !numels) return 16;
+  constexpr int tile = tile_of<float, SumSqOp>();  // the float32 tile is the smallest
+  return align_up((size_t)n * sizeof(float), 16) + (size_t)count_tiles(n, numels, tile) * sizeof(double) + 16;
+}
+
+void optimi_b200_grad_scale_begin(const float* device_factor) { g_grad_factor = device_factor; }
+
+void optimi_b200_grad_scale_end(void) { g_grad_factor = nullptr; }
+
+int optimi_b200_grad_clip_factor(int n, void* const* grads, const int64_t* numels, int dtype, double max_norm, float* out,
+                                 void* workspace, size_t workspace_bytes, void* stream) {
+  const char* fn = "optimi_b200_grad_clip_factor";
+  void* const* const lists[2] = {grads, nullptr};
+  const bool req[2] = {true, false};
+  static const char* const names[2] = {"grads", ""};
+  int rc = check_lists(fn, n, numels, dtype, 2, lists, req, names);
+  if (rc != OPTIMI_OK) return rc;
+  if (!out) return fail(OPTIMI_ERR_INVALID_ARGUMENT, "%s: out is NULL", fn);
+  if (n == 0) return fail(OPTIMI_ERR_INVALID_ARGUMENT, "%s: no tensors", fn);
+  const size_t need = optimi_b200_grad_clip_workspace_bytes(n, numels) - 16;
+  if (!workspace || workspace_bytes < need)
+    return fail(OPTIMI_ERR_WORKSPACE_TOO_SMALL, "%s: workspace of %zu bytes given, %zu needed", fn,
+                workspace ? workspace_bytes : (size_t)0, need);
+  if (reinterpret_cast<uintptr_t>(workspace) & 15) return fail(OPTIMI_ERR_INVALID_ARGUMENT, "%s: workspace is not 16-byte aligned", fn);
+  float* tensor_norms = reinterpret_cast<float*>(workspace);
+  double* partial = reinterpret_cast<double*>(reinterpret_cast<char*>(workspace) + align_up((size_t)n * sizeof(float), 16));
+  cudaStream_t s = (cudaStream_t)stream;
+  auto typed = [&](auto tag) {
+    using T = decltype(tag);
+    auto pass = [&](auto small) {
+      constexpr bool SMALL = decltype(small)::value;
+      return for_each_table<2, SMALL>(n, numels, lists, tile_of<T, SumSqOp>(), [&](const MtaTable<2, SMALL>& tab, int tiles) {
+        int r = launch_kernel(fn, tile_sum_kernel<T, SumSqOp, SMALL>, tiles, kThreads, s, tab, SumSqArgs{}, partial);
+        if (r != OPTIMI_OK) return r;
+        const double* partial_in = partial;
+        return launch_kernel(fn, norm_finalize_kernel<T, SMALL>, tab.n_tensors, 256, s, tab, partial_in, tensor_norms);
+      });
+    };
+    // tensors without elements launch nothing: their norm is zero
+    if (g_graph.mode != kGraphUpdate) {
+      cudaError_t e = cudaMemsetAsync(tensor_norms, 0, (size_t)n * sizeof(float), s);
+      if (e != cudaSuccess) return fail(OPTIMI_ERR_CUDA, "%s: cudaMemsetAsync: %s", fn, cudaGetErrorString(e));
+    }
+    int r = n <= MtaTable<2, true>::CAP ? pass(std::true_type{}) : pass(std::false_type{});
+    if (r != OPTIMI_OK) return r;
+    const float* norms_in = tensor_norms;
+    return launch_kernel(fn, clip_factor_kernel<T>, 1, 256, s, norms_in, n, (float)max_norm, out);
+  };
+  switch (dtype) {
+    case OPTIMI_F32: return typed(float{});
+    case OPTIMI_BF16: return typed(__nv_bfloat16{});
+    default: return typed(__half{});
   }
 }
 

@@ -72,6 +72,7 @@ struct OpBase {
   static constexpr bool kPush = false;
   static constexpr int kPull = 0;
   static constexpr bool kWholeTileBranch = false;
+  static constexpr int kGradSlot = 1;  // the list that holds the gradients
   template <class Table, class Args>
   static __device__ __forceinline__ NoCtx context(const Table&, const Span&, const Args&) { return NoCtx{}; }
 };
@@ -141,6 +142,60 @@ struct PeerOp {
   static __device__ __forceinline__ bool writes(int l, const Args& a) { return Base::writes(l, a.base); }
   template <typename T>
   static __device__ __forceinline__ void elem(float (&e)[NL], const Args& a, const Ctx& ctx) { Base::template elem<T>(e, a.base, ctx); }
+};
+
+// Any op with its gradients multiplied, as they are loaded, by one fp32 factor read from device
+// memory: g <- round(g * factor), the arithmetic of `torch._foreach_mul_(grads, factor_tensor)`
+// (what clip_grad_norm_ and GradScaler.unscale_ do to the gradients in a pass of their own).  The
+// scaled gradient exists only in registers; the gradient buffer is not written.
+template <class BaseArgs>
+struct ScaledArgs {
+  BaseArgs base;
+  const float* factor;  // device
+};
+
+template <class Base>
+struct ScaledOp {
+  static constexpr int NL = Base::NL, U = Base::U, kSumSlot = Base::kSumSlot, kMinBlocks = Base::kMinBlocks;
+  static constexpr bool kPush = false;
+  static constexpr int kPull = 0;
+  static constexpr bool kWholeTileBranch = Base::kWholeTileBranch;
+  static constexpr int kGradSlot = Base::kGradSlot;
+  using Args = ScaledArgs<typename Base::Args>;
+  struct Ctx {
+    typename Base::Ctx base;
+    float factor;
+  };
+  template <class Table>
+  static __device__ __forceinline__ Ctx context(const Table& tab, const Span& s, const Args& a) {
+    return Ctx{Base::context(tab, s, a.base), __ldg(a.factor)};
+  }
+  static __device__ __forceinline__ bool reads(int l, const Args& a) { return Base::reads(l, a.base); }
+  static __device__ __forceinline__ bool writes(int l, const Args& a) { return Base::writes(l, a.base); }
+  template <typename T>
+  static __device__ __forceinline__ void elem(float (&e)[NL], const Args& a, const Ctx& ctx) {
+    e[kGradSlot] = rnd<T>(__fmul_rn(e[kGradSlot], ctx.factor));
+    Base::template elem<T>(e, a.base, ctx.base);
+  }
+};
+
+// ---------------------------------------------------------------------------------------------
+// Sum of squares of a gradient list (the first pass of a gradient-norm clip)
+// lists: 0 g, 1 (pseudo, no memory) carries g^2 out for the tile sum
+// ---------------------------------------------------------------------------------------------
+struct SumSqArgs {};
+struct SumSqOp : OpBase {
+  static constexpr int NL = 2, U = OPTIMI_U_NARROW;
+  static constexpr int kSumSlot = 1;
+  static constexpr int kMinBlocks = 12;
+  static constexpr int kGradSlot = 0;
+  using Args = SumSqArgs;
+  static __device__ __forceinline__ bool reads(int l, const Args&) { return l == 0; }
+  static __device__ __forceinline__ bool writes(int, const Args&) { return false; }
+  template <typename T>
+  static __device__ __forceinline__ void elem(float (&e)[NL], const Args&, const NoCtx&) {
+    e[1] = __fmul_rn(e[0], e[0]);
+  }
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -342,6 +397,7 @@ struct StableMomentsOp : OpBase {
   static constexpr int NL = 4, U = OPTIMI_U_NARROW;
   static constexpr int kMinBlocks = kStableMinBlocks;
   static constexpr bool kWholeTileBranch = true;
+  static constexpr int kGradSlot = 0;
   static constexpr int kSumSlot = REDUCE ? 3 : -1;
   using Args = StableMomentsArgs;
   static __device__ __forceinline__ bool reads(int l, const Args&) { return l != 3; }

@@ -191,6 +191,9 @@ class OptimiOptimizer(Optimizer):
         self._release_stream: torch.cuda.Stream | None = None
         self._release_fence_queued = False
         self._graph_nodes: _lib.GraphNodes | None = None  # kernel nodes of the step captured into a CUDA graph
+        self._grad_factor: Tensor | None = None  # device scalar the next step(s) multiply the gradients by
+        self._grad_factor_once = False  # set by clip_grad_norm: the factor belongs to the next step only
+        self._clip_out: Tensor | None = None  # (factor, total norm) written by clip_grad_norm
 
         if self.defaults["gradient_release"]:
             if self.defaults["foreach"]:
@@ -262,15 +265,80 @@ class OptimiOptimizer(Optimizer):
             with torch.enable_grad():
                 loss = closure()
 
-        if param is None:
+        if param is not None:
+            self._release(param)
+            return loss
+        factor = self._grad_factor
+        if factor is not None:
+            _lib.LIB.optimi_b200_grad_scale_begin(factor.data_ptr())
+        try:
             if torch.cuda.is_initialized() and torch.cuda.is_current_stream_capturing():
                 self._capture_step()
             else:
                 for group in self.param_groups:
                     self._step_group(group)
-        else:
-            self._release(param)
+        finally:
+            if factor is not None:
+                _lib.LIB.optimi_b200_grad_scale_end()
+                if self._grad_factor_once:
+                    self._grad_factor = None
         return loss
+
+    # ---- gradient scaling fused into the step ----------------------------------------------------
+    def set_grad_factor(self, factor: Tensor | None) -> None:
+        """From now on every step multiplies each gradient element by `factor` (a CUDA float32 tensor with
+        one element, read on the device when the step runs) as it loads it: `g <- round(g * factor)`, what
+        `torch._foreach_mul_(grads, factor)` would have done in a pass of its own — a GradScaler's inverse
+        scale, a clip coefficient computed elsewhere.  The gradients themselves are left as they are.
+        `None` switches it off.  Also applies to gradient-release steps."""
+        if factor is not None and (factor.dtype != torch.float32 or not factor.is_cuda or factor.numel() != 1):
+            raise ValueError("set_grad_factor: the factor must be a CUDA float32 tensor with one element")
+        self._grad_factor, self._grad_factor_once = factor, False
+
+    @torch.no_grad()
+    def clip_grad_norm(self, max_norm: float) -> Tensor:
+        """`torch.nn.utils.clip_grad_norm_(params, max_norm)` without touching the gradients: computes
+        the total 2-norm of all gradients and the clip coefficient `min(1, max_norm / (norm + 1e-6))`
+        on the device (one read of the gradients, PyTorch's own order of roundings), and makes the
+        NEXT `step()` scale the gradients by the coefficient as it loads them.  Returns the total norm
+        as a 0-dim CUDA tensor (no host synchronisation).  Saves the read-modify-write pass over the
+        gradients that clipping in place costs.  All gradients must share one device and dtype; not
+        for gradient release, where parameters are stepped before all gradients exist."""
+        if self.defaults.get("gradient_release", False):
+            raise RuntimeError("clip_grad_norm needs all gradients before any parameter is stepped: not with gradient_release")
+        grads = [p.grad for group in self.param_groups for p in group["params"] if p.grad is not None]
+        if not grads:
+            raise RuntimeError("clip_grad_norm: no parameter has a gradient")
+        g0 = grads[0]
+        if not g0.is_cuda or g0.dtype not in _lib.DTYPE_CODE:
+            raise RuntimeError("clip_grad_norm: gradients must be CUDA float32, bfloat16 or float16 tensors")
+        for g in grads:
+            if g.device != g0.device or g.dtype != g0.dtype:
+                raise NotImplementedError("clip_grad_norm: all gradients must share one device and dtype")
+            if not g.is_contiguous() and not torch._prims_common.is_non_overlapping_and_dense(g):
+                raise RuntimeError("clip_grad_norm: gradients must be dense")
+        if self._clip_out is None or self._clip_out.device != g0.device:
+            self._clip_out = torch.zeros(2, dtype=torch.float32, device=g0.device)
+        numels = _lib.numel_array(grads)
+        numels_arg = ctypes.cast(numels, ctypes.c_void_p)
+        need = _lib.LIB.optimi_b200_grad_clip_workspace_bytes(len(grads), numels_arg)
+        stream_ptr = torch._C._cuda_getCurrentRawStream(g0.device.index)
+        ws = F._stable_workspace(g0.device, stream_ptr, need)
+        ptrs = _lib.PointerArray(grads)
+        capturing = torch.cuda.is_current_stream_capturing()
+        record = _lib.graph_record() if capturing else None  # nothing in these launches changes from step to step
+        with torch.cuda.device(g0.device):
+            if record is not None:
+                record.__enter__()
+            try:
+                rc = _lib.LIB.optimi_b200_grad_clip_factor(len(grads), ptrs.ptr, numels_arg, _lib.DTYPE_CODE[g0.dtype], float(max_norm),
+                                                           self._clip_out.data_ptr(), ws.data_ptr(), ws.numel(), stream_ptr)  # fmt: skip
+            finally:
+                if record is not None:
+                    record.__exit__(None, None, None)
+        _lib.check(rc)
+        self._grad_factor, self._grad_factor_once = self._clip_out[:1], not capturing
+        return self._clip_out[1]
 
     # ---- the step inside a CUDA graph -----------------------------------------------------------
     def _capture_step(self) -> None:
@@ -312,9 +380,16 @@ class OptimiOptimizer(Optimizer):
             raise RuntimeError("update_graph: no captured step to update; call step() under torch.cuda.graph(...) first")
         graph.raw_cuda_graph()  # raises unless the graph was created with keep_graph=True
         graph_exec = graph.raw_cuda_graph_exec()
-        with torch.no_grad(), _lib.graph_update(self._graph_nodes, graph_exec):
-            for group in self.param_groups:
-                self._step_group(group)
+        factor = self._grad_factor
+        if factor is not None:
+            _lib.LIB.optimi_b200_grad_scale_begin(factor.data_ptr())
+        try:
+            with torch.no_grad(), _lib.graph_update(self._graph_nodes, graph_exec):
+                for group in self.param_groups:
+                    self._step_group(group)
+        finally:
+            if factor is not None:
+                _lib.LIB.optimi_b200_grad_scale_end()
 
     # ---- whole-list step of one parameter group ---------------------------------------------------
     def _step_group(self, group: dict[str, Any], capturing: bool = False) -> None:
@@ -388,11 +463,16 @@ class OptimiOptimizer(Optimizer):
         stream_ptr = side.cuda_stream if side is not None else torch._C._cuda_getCurrentRawStream(plan.index)
         if self._needs_workspace:
             tail = tail + (F.stable_workspace_args(plan.device, stream_ptr, (param,)) if update else (None, 0))
+        factor = self._grad_factor
+        if factor is not None:
+            _lib.LIB.optimi_b200_grad_scale_begin(factor.data_ptr())
         if torch._C._cuda_getDevice() == plan.index:
             rc = plan.fn(1, *plan.args, plan.numels_arg, plan.dtype_code, *tail, stream_ptr)
         else:
             with torch.cuda.device(plan.device):
                 rc = plan.fn(1, *plan.args, plan.numels_arg, plan.dtype_code, *tail, stream_ptr)
+        if factor is not None:
+            _lib.LIB.optimi_b200_grad_scale_end()
         if rc != 0:
             _lib.check(rc)
         if side is not None:

@@ -93,3 +93,23 @@ def test_graph_brackets_reject_misuse_without_touching_the_device():
     assert L.optimi_b200_graph_update_begin(out, None) == -1 and b"graph_exec is NULL" in L.optimi_b200_last_error()
     L.optimi_b200_graph_nodes_free(out)
     L.optimi_b200_graph_nodes_free(None)
+
+
+def test_grad_clip_factor_checks_its_arguments():
+    from optimi_b200 import _lib
+
+    L = _lib.LIB
+    before = L.optimi_b200_launch_count()
+    one = (ctypes.c_int64 * 1)(4096)
+    numels = ctypes.cast(one, ctypes.c_void_p)
+    arr = (ctypes.c_void_p * 1)(0x1000)
+    lst = ctypes.cast(arr, ctypes.c_void_p)
+    need = L.optimi_b200_grad_clip_workspace_bytes(1, numels)
+    assert need >= 16 + 8 * (4096 // 512)
+    fake = ctypes.c_void_p(0x2000)
+    assert L.optimi_b200_grad_clip_factor(1, lst, numels, 1, 1.0, None, fake, need, None) == -1
+    assert b"out is NULL" in L.optimi_b200_last_error()
+    assert L.optimi_b200_grad_clip_factor(1, lst, numels, 1, 1.0, fake, fake, 8, None) == -3
+    assert b"workspace" in L.optimi_b200_last_error()
+    assert L.optimi_b200_grad_clip_factor(1, None, numels, 1, 1.0, fake, fake, need, None) == -1
+    assert L.optimi_b200_launch_count() == before
