@@ -185,9 +185,12 @@ struct ScaledOp {
 // ---------------------------------------------------------------------------------------------
 struct SumSqArgs {};
 struct SumSqOp : OpBase {
-  static constexpr int NL = 2, U = OPTIMI_U_NARROW;
+  // one stream, read only: four vectors per thread in flight (8 KB per block), or the per-block cost
+  // of the reduction dominates (one vector per thread measured 2.9 TB/s)
+  static constexpr int NL = 2, U = 4;
   static constexpr int kSumSlot = 1;
   static constexpr int kMinBlocks = 12;
+  static constexpr bool kWholeTileBranch = true;
   static constexpr int kGradSlot = 0;
   using Args = SumSqArgs;
   static __device__ __forceinline__ bool reads(int l, const Args&) { return l == 0; }

@@ -225,6 +225,14 @@ class OptimiOptimizer(Optimizer):
         """Creates the optimizer-specific state tensors of `param` (subclass hook)."""
         raise NotImplementedError
 
+    def _first_gradient(self, param: Tensor) -> Tensor:
+        """A copy of `param.grad` as the step kernels will see it — times the gradient factor when one is set —
+        for the states that start from the first gradient (Adan's previous gradient, SGD's `torch_init`)."""
+        grad = param.grad.detach()
+        if self._grad_factor is None:
+            return grad.clone()
+        return (grad.float() * self._grad_factor.to(grad.device)).to(grad.dtype)  # fp32 product, one rounding: the kernels' arithmetic
+
     def _kahan_state(self, group: dict[str, Any], param: Tensor) -> Tensor | None:
         """Kahan compensation buffer: on by default for bf16/fp16 parameters (`kahan_sum=None`),
         never for float32 (e.g. optimi/adam.py:100-106)."""
@@ -721,7 +729,7 @@ class SGD(OptimiOptimizer):
     def _new_state(self, group, state, param):
         if group["dampening"] and group["torch_init"]:
             # torch.optim.SGD seeds the buffer with the gradient after L2 decay (optimi/sgd.py:101-105)
-            state["exp_avg"] = param.grad.detach().clone()
+            state["exp_avg"] = self._first_gradient(param)
             if group["weight_decay"] != 0 and not group["decouple_lr"] and not group["decouple_wd"]:
                 state["exp_avg"].add_(param, alpha=group["weight_decay"])
         elif group["momentum"] != 0:
@@ -808,7 +816,7 @@ class Adan(OptimiOptimizer):
         state["exp_avg_diff"] = torch.zeros_like(param, memory_format=torch.preserve_format)
         state["exp_avg_sq"] = torch.zeros_like(param, memory_format=torch.preserve_format)
         # negated first gradient, so the first gradient difference is zero (optimi/adan.py:109)
-        state["prev_grad"] = param.grad.clone().mul_(-1)
+        state["prev_grad"] = self._first_gradient(param).mul_(-1)
 
     def _setup_group(self, group):
         first = not group["setup"]
