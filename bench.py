@@ -381,6 +381,11 @@ def run_b200_arm(args):
     total_ms = ev[0][0].elapsed_time(ev[-1][2])
     step_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / args.steps
     gather_ms = sum(e[1].elapsed_time(e[2]) for e in ev) / args.steps
+    # spread of the whole step (local step + exchange) over the timed steps of this rank, as the reference's own
+    # benchmark reports it (mean / median / p90, examples/benchmark.py:373-381)
+    per_step = sorted(e[0].elapsed_time(e[2]) for e in ev)
+    spread = {"mean": sum(per_step) / len(per_step), "median": per_step[len(per_step) // 2],
+              "p90": per_step[min(len(per_step) - 1, int(0.9 * len(per_step)))], "min": per_step[0], "max": per_step[-1]}  # fmt: skip
     total_ms = max_over_ranks(total_ms, world, device)
     step_ms_max = max_over_ranks(step_ms, world, device)
     gather_ms_max = max_over_ranks(gather_ms, world, device)
@@ -461,6 +466,7 @@ def run_b200_arm(args):
         "config": make_config(args.workload, world, args.exchange, args.optimizer),
         "exchange": None if sharded is None else sharded.exchange, "reduce_grads": bool(args.reduce_grads),
         "hbm_gbs": achieved, "step_ms": step_ms_max, "gather_ms": gather_ms_max, "wall_ms_per_step": t_wall * 1e3 / args.steps,
+        "step_ms_spread_rank0": spread,
         "roofline": roofline, "nvlink": nvlink, "cpu_baseline": cpu,
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
                 "ms_per_step": e2e_s * 1e3, "steps": e2e_steps},
