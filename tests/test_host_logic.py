@@ -207,3 +207,23 @@ def test_empty_step_advances_the_group_counter_like_the_reference():
     opt = optimi_b200.Adam([p], lr=1e-3)
     opt.step()
     assert int(opt.param_groups[0]["step"]) == 1 and opt.param_groups[0]["setup"]
+
+
+def test_grad_factor_and_graph_entry_points_validate_on_the_host():
+    import optimi_b200
+
+    p = torch.nn.Parameter(torch.zeros(8))
+    opt = optimi_b200.AdamW([p], lr=1e-3)
+    with pytest.raises(ValueError, match="CUDA float32"):
+        opt.set_grad_factor(torch.ones(1))  # a CPU tensor
+    opt.set_grad_factor(None)
+    with pytest.raises(RuntimeError, match="no parameter has a gradient"):
+        opt.clip_grad_norm(1.0)
+    p.grad = torch.ones(8)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        opt.clip_grad_norm(1.0)
+    with pytest.raises(RuntimeError, match="no captured step"):
+        opt.update_graph(None)
+    released = optimi_b200.AdamW([p], lr=1e-3, gradient_release=True)
+    with pytest.raises(RuntimeError, match="gradient_release"):
+        released.clip_grad_norm(1.0)
