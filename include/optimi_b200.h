@@ -103,8 +103,9 @@ int optimi_b200_graph_update_end(void);
  * out[1] = total, the 2-norm of all gradients, to the DEVICE array `out` (2 floats), following
  * clip_grad_norm_'s own order of operations and roundings (per-tensor norms in the storage type,
  * their 2-norm, reciprocal, product, clamp).  One read of the gradients; sums are taken in double
- * in a fixed order, so the result is deterministic and agrees with PyTorch's up to the rounding of
- * its fp32 sums (at most one unit of the storage type in the factor).  `workspace`: DEVICE scratch of
+ * in a fixed order, so the result is deterministic and agrees with PyTorch's up to the rounding error of
+ * its fp32 sums (bf16 / fp16: at most one unit of the storage type; fp32: a relative 1e-6 or so).
+ * `workspace`: DEVICE scratch of
  * optimi_b200_grad_clip_workspace_bytes(n_tensors, numels) bytes, 16-byte aligned. */
 void optimi_b200_grad_scale_begin(const float* device_factor);
 void optimi_b200_grad_scale_end(void);

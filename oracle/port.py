@@ -240,3 +240,44 @@ def _fma_round(g: torch.Tensor, p: torch.Tensor, alpha: float) -> torch.Tensor:
     """round_to_dtype(fma(fp32(alpha), p, g)) — ``g.add_(p, alpha=alpha)`` as one fused op."""
     a = float(torch.tensor(alpha, dtype=torch.float32))
     return (g.double() + a * p.double()).float().to(g.dtype)
+
+
+# ------------------------------------------------------------------------------------------------
+# Gradient scaling next to the step.  These restate PyTorch, not the reference (which leaves
+# clipping and loss-scale unscaling to its callers): torch/nn/utils/clip_grad.py `_get_total_norm`
+# and `_clip_grads_with_norm_`, and the arithmetic of `torch._foreach_mul_(grads, scalar_tensor)`.
+# ------------------------------------------------------------------------------------------------
+def scale_gradient(grad: torch.Tensor, factor: float) -> torch.Tensor:
+    """`grad * factor` as `_foreach_mul_` with a 0-dim tensor computes it: fp32 product of the element and
+    the fp32 factor, one rounding to the gradient's dtype."""
+    f = torch.tensor(factor, dtype=torch.float32)
+    return (grad.float() * f).to(grad.dtype)
+
+
+def clip_factor(grads: list[torch.Tensor], max_norm: float) -> tuple[float, float]:
+    """(coefficient, total norm) of `torch.nn.utils.clip_grad_norm_(params, max_norm)` for gradients of one dtype,
+    every intermediate rounded to that dtype as PyTorch's tensor arithmetic rounds it:
+
+        norms  = [round(sqrt(sum g^2)) for g in grads]            torch._foreach_norm
+        total  = round(sqrt(sum norms^2))                          torch.linalg.vector_norm(torch.stack(norms))
+        coef   = round(round(1 / round(total + 1e-6)) * max_norm)  Tensor.__rtruediv__ is reciprocal() * other
+        coef   = min(coef, 1)                                      torch.clamp(max=1.0), NaN kept
+
+    Sums of squares are taken in double here, so results can differ from PyTorch's fp32 sums by one unit of
+    the dtype."""
+    dtype = grads[0].dtype
+
+    def rnd(x: float) -> float:
+        return float(torch.tensor(x, dtype=torch.float32).to(dtype))
+
+    def f32(x: float) -> float:
+        return float(torch.tensor(x, dtype=torch.float32))
+
+    norms = [rnd(f32(math.sqrt(f32(float(g.double().square().sum()))))) for g in grads]
+    total = rnd(f32(math.sqrt(f32(sum(n * n for n in norms)))))
+    denom = rnd(f32(total + f32(1e-6)))
+    recip = rnd(f32(1.0 / denom)) if denom != 0 else float("inf")
+    coef = rnd(f32(recip * f32(max_norm)))
+    if coef > 1.0:
+        coef = 1.0
+    return coef, total

@@ -66,3 +66,35 @@ def test_oracle_config1_matches_reference_on_cpu():
             # parameters that pass close to zero get an absolute floor of 1e-6 of the weights' scale (0.02 .. 0.1)
             atol = 1e-7 if name == "param" else 1e-10
             assert _rel_close(t.reshape(-1)[::CONFIG1_STRIDE], want, 1e-6, atol), f"tensor {i} {name}"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("max_norm", [0.05, 1.0, 1e4])
+def test_oracle_clip_factor_matches_pytorch_on_cpu(dtype, max_norm):
+    """The oracle's restatement of clip_grad_norm_'s coefficient against PyTorch itself (CPU tensors)."""
+    from oracle import port
+
+    gen = torch.Generator().manual_seed(11)
+    shapes = [(257, 129), (4096,), (1000, 333), (7,), (300, 1024)]
+    grads = [(torch.randn(s, generator=gen) * 1e-2).to(dtype) for s in shapes]
+    params = []
+    for g in grads:
+        p = torch.nn.Parameter(torch.zeros_like(g))
+        p.grad = g.clone()
+        params.append(p)
+    total = torch.nn.utils.clip_grad_norm_(params, max_norm)
+    coef = torch.clamp(max_norm / (total + 1e-6), max=1.0)
+    o_coef, o_total = port.clip_factor(grads, max_norm)
+
+    def tol(x):
+        # bf16: one unit in the last place.  float32: PyTorch's CPU sum of a few hundred thousand fp32 squares
+        # carries a relative error of order 1e-6, the oracle sums in double
+        import math
+
+        return 2.0 ** (math.floor(math.log2(abs(x))) - 7) if dtype == torch.bfloat16 else 2e-5 * abs(x)
+
+    assert abs(o_total - float(total)) <= tol(float(total))
+    assert abs(o_coef - float(coef)) <= tol(float(coef))
+    if o_coef == float(coef):
+        for p, g in zip(params, grads):
+            assert torch.equal(p.grad, port.scale_gradient(g, o_coef))
