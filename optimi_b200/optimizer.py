@@ -346,7 +346,7 @@ class OptimiOptimizer(Optimizer):
                     record.__exit__(None, None, None)
         _lib.check(rc)
         self._grad_factor, self._grad_factor_once = self._clip_out[:1], not capturing
-        return self._clip_out[1]
+        return self._clip_out[1].clone()  # the two-float buffer is reused by the next call
 
     # ---- the step inside a CUDA graph -----------------------------------------------------------
     def _capture_step(self) -> None:
