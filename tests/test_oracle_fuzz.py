@@ -1,0 +1,48 @@
+"""Pins the CPU oracle against what the unmodified reference computed (CPU, float32, foreach path) for 64
+seeded random optimizer / hyper-parameter / learning-rate-schedule combinations — the configurations
+the fixed golden cases do not reach (betas of 0 and 0.999, eps down to 1e-10, dampening with
+`torch_init`, lookahead every step, zero gradients, one-element tensors)."""
+
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden"))
+from make_fuzz_golden import N_SEEDS, fuzz_inputs  # noqa: E402
+
+from cases import STATE_NAMES  # noqa: E402
+
+GOLDEN = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "cpu_fuzz_f32.npz"))
+
+
+@pytest.mark.parametrize("seed", range(N_SEEDS))
+def test_oracle_matches_reference_on_random_float32_configurations(seed):
+    from oracle.port import OracleOptimizer
+
+    opt, kw, params, grads, lrs = fuzz_inputs(seed)
+    oracle = OracleOptimizer(opt, [p.clone() for p in params], **kw)
+    for it, gs in enumerate(grads):
+        oracle.h["lr"] = lrs[it]
+        oracle.step([g.clone() for g in gs])
+    checked = 0
+    for i, p in enumerate(oracle.params):
+        if p.numel() == 0:
+            continue
+        pairs = [("param", p)]
+        for name in STATE_NAMES[opt]:
+            t = oracle.state[i].get(name)
+            if t is not None and t.numel() == p.numel():
+                pairs.append((name, t))
+        for name, got in pairs:
+            want = torch.from_numpy(GOLDEN[f"fuzz{seed}/{i}.{name}"].copy()).double().reshape(-1)
+            got = got.double().reshape(-1)
+            # CPU ATen neither fuses multiply-adds nor divides by reciprocals the way CUDA ATen (which the
+            # oracle follows) does: 1e-6 relative per op, a few of them chained, over a floor of 1e-6 of the tensor's scale
+            tol = 5e-6 * want.abs() + 1e-6 * float(want.abs().max()) + 1e-30
+            bad = (got - want).abs() > tol
+            assert not bool(bad.any()), f"seed {seed} {opt} {kw} tensor {i} {name}: {int(bad.sum())}/{bad.numel()} off, worst {float(((got - want).abs() / tol).max()):.1f}x"
+            checked += 1
+    assert checked or all(p.numel() == 0 for p in oracle.params)
