@@ -46,3 +46,42 @@ def test_oracle_matches_reference_on_random_float32_configurations(seed):
             assert not bool(bad.any()), f"seed {seed} {opt} {kw} tensor {i} {name}: {int(bad.sum())}/{bad.numel()} off, worst {float(((got - want).abs() / tol).max()):.1f}x"
             checked += 1
     assert checked or all(p.numel() == 0 for p in oracle.params)
+
+
+CUDA_FUZZ_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "cuda_fuzz.npz")
+
+
+@pytest.mark.skipif(not os.path.exists(CUDA_FUZZ_PATH), reason="tests/golden/cuda_fuzz.npz has not been generated (make_fuzz_golden.py --device cuda)")
+@pytest.mark.parametrize("seed", range(N_SEEDS))
+def test_oracle_matches_reference_on_random_configurations_from_a_gpu(seed):
+    """Same configurations in their own storage types (bf16 / fp16 / fp32, Kahan as drawn) against what the
+    reference's foreach path produced on a CUDA device: bit for bit, StableAdamW at its stated tolerance."""
+    from helpers import ulp_diff
+    from oracle.port import OracleOptimizer
+
+    golden = np.load(CUDA_FUZZ_PATH)
+    opt, kw, params, grads, lrs = fuzz_inputs(seed, float32_only=False)
+    oracle = OracleOptimizer(opt, [p.clone() for p in params], **kw)
+    for it, gs in enumerate(grads):
+        oracle.h["lr"] = lrs[it]
+        oracle.step([g.clone() for g in gs])
+    for i, p in enumerate(oracle.params):
+        if p.numel() == 0:
+            continue
+        pairs = [("param", p)]
+        for name in STATE_NAMES[opt]:
+            t = oracle.state[i].get(name)
+            if t is not None and t.numel() == p.numel():
+                pairs.append((name, t))
+        for name, got in pairs:
+            raw = golden[f"fuzz{seed}/{i}.{name}"]
+            want = torch.from_numpy(raw.copy()) if got.dtype == torch.float32 else torch.from_numpy(raw.view(np.int16).copy()).view(got.dtype)
+            got, want = got.reshape(-1), want.reshape(-1)
+            where = f"seed {seed} {opt} {kw} tensor {i} {name}"
+            if opt == "stableadamw":
+                ok = (got.double() - want.double()).abs() <= 1e-6 + (2e-6 if got.dtype == torch.float32 else 2**-7) * want.double().abs()
+                assert bool(ok.all()), f"{where}: {int((~ok).sum())} elements off"
+            else:
+                d = ulp_diff(got, want)
+                d[got.isnan() & want.isnan()] = 0
+                assert int(d.max()) == 0, f"{where}: {int((d > 0).sum())}/{d.numel()} differ, max {int(d.max())} ulp"
