@@ -398,6 +398,8 @@ class OptimiOptimizer(Optimizer):
         finally:
             if factor is not None:
                 _lib.LIB.optimi_b200_grad_scale_end()
+                if self._grad_factor_once:  # an eager clip_grad_norm() before this replay: its coefficient is for this step only
+                    self._grad_factor = None
 
     # ---- whole-list step of one parameter group ---------------------------------------------------
     def _step_group(self, group: dict[str, Any], capturing: bool = False) -> None:
