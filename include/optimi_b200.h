@@ -97,7 +97,7 @@ int optimi_b200_graph_update_end(void);
  * torch._foreach_mul_(grads, factor_tensor) — and steps with that.  The gradient buffers are not
  * written.  The value is read when the kernels run, so it may be produced on the same stream just
  * before (optimi_b200_grad_clip_factor below, or a GradScaler's inverse scale).  Not combinable
- * with the peer push / pull brackets.
+ * with the gradient pull bracket (the peer push composes with it).
  *
  * optimi_b200_grad_clip_factor: writes out[0] = min(1, max_norm * (1 / (total + 1e-6))) and
  * out[1] = total, the 2-norm of all gradients, to the DEVICE array `out` (2 floats), following
@@ -112,6 +112,25 @@ void optimi_b200_grad_scale_end(void);
 size_t optimi_b200_grad_clip_workspace_bytes(int n_tensors, const int64_t* numels);
 int optimi_b200_grad_clip_factor(int n_tensors, void* const* grads, const int64_t* numels, int dtype, double max_norm,
                                  float* out, void* workspace, size_t workspace_bytes, void* stream);
+
+/* The same clip factor in separable steps, for gradients that one call cannot see whole: tensors cut
+ * into pieces that live on several ranks (ZeRO-1 sharding), or lists of several dtypes (float32
+ * embeddings beside a bfloat16 body, as optimi's to_low_precision leaves a model:
+ * optimi/utils.py:104-169).  No counterpart in the reference.
+ *
+ * optimi_b200_grad_sumsq: sumsq[i] (DEVICE, n_tensors doubles) = sum of squares of tensor (or piece) i,
+ * in double, in a fixed order.  `workspace` as for optimi_b200_grad_clip_factor.  The caller adds up the
+ * pieces of one tensor (and the ranks' contributions) as it sees fit.
+ * optimi_b200_grad_norms_from_sumsq: norms[i] (DEVICE floats) = sqrt((float)sumsq[i]) rounded to the
+ * storage type `dtype`, what torch._foreach_norm returns for a tensor of that dtype.
+ * optimi_b200_clip_factor_from_norms: out[0] = min(1, max_norm * (1 / (total + 1e-6))), out[1] = total
+ * = the 2-norm of `norms`, every intermediate rounded to `dtype` — the dtype torch promotes the stacked
+ * norms to: the gradients' own if they share one, float32 otherwise. */
+int optimi_b200_grad_sumsq(int n_tensors, void* const* grads, const int64_t* numels, int dtype, double* sumsq,
+                           void* workspace, size_t workspace_bytes, void* stream);
+int optimi_b200_grad_norms_from_sumsq(int n_tensors, const double* sumsq, int dtype, float* norms, void* stream);
+int optimi_b200_clip_factor_from_norms(int n_tensors, const float* norms, int dtype, double max_norm, float* out,
+                                       void* stream);
 
 /* Adam / AdamW.  Replaces _foreach_adam (optimi/adam.py:399-453), _single_param_adam
  * (optimi/adam.py:354-396) and the Triton launchers (optimi/adam.py:533-630); called where

@@ -8,14 +8,10 @@ own message.
 from __future__ import annotations
 
 import ctypes
-import os
 
 import torch
 
 from . import build as _build
-
-# OPTIMI_B200_LIBRARY: load this prebuilt library instead of the in-tree one (kernel tuning runs)
-_OVERRIDE = os.environ.get("OPTIMI_B200_LIBRARY")
 
 OPTIMI_F32, OPTIMI_BF16, OPTIMI_F16 = 0, 1, 2
 DTYPE_CODE = {torch.float32: OPTIMI_F32, torch.bfloat16: OPTIMI_BF16, torch.float16: OPTIMI_F16}
@@ -39,12 +35,13 @@ EXPORTS = list(SIGNATURES) + ["optimi_b200_push_begin", "optimi_b200_push_end", 
                                    "optimi_b200_graph_record_begin", "optimi_b200_graph_record_end", "optimi_b200_graph_nodes_count",
                                    "optimi_b200_graph_nodes_free", "optimi_b200_graph_update_begin", "optimi_b200_graph_update_end",
                                    "optimi_b200_grad_scale_begin", "optimi_b200_grad_scale_end", "optimi_b200_grad_clip_workspace_bytes",
-                                   "optimi_b200_grad_clip_factor"]  # fmt: skip
+                                   "optimi_b200_grad_clip_factor", "optimi_b200_grad_sumsq", "optimi_b200_grad_norms_from_sumsq",
+                                   "optimi_b200_clip_factor_from_norms"]  # fmt: skip
 
 
 def _load() -> ctypes.CDLL:
-    path = _OVERRIDE or _build.LIB
-    if not _OVERRIDE and not _build.up_to_date():
+    path = _build.LIB
+    if not _build.up_to_date():
         # not built yet, or built from other sources: build now (needs nvcc), else fail loudly
         path = _build.build(force=True)
     lib = ctypes.CDLL(path)
@@ -75,6 +72,12 @@ def _load() -> ctypes.CDLL:
     lib.optimi_b200_grad_clip_workspace_bytes.argtypes = [_I, _P]
     lib.optimi_b200_grad_clip_factor.restype = _I
     lib.optimi_b200_grad_clip_factor.argtypes = [_I, _P, _P, _I, _D, _P, _P, ctypes.c_size_t, _P]
+    lib.optimi_b200_grad_sumsq.restype = _I
+    lib.optimi_b200_grad_sumsq.argtypes = [_I, _P, _P, _I, _P, _P, ctypes.c_size_t, _P]
+    lib.optimi_b200_grad_norms_from_sumsq.restype = _I
+    lib.optimi_b200_grad_norms_from_sumsq.argtypes = [_I, _P, _I, _P, _P]
+    lib.optimi_b200_clip_factor_from_norms.restype = _I
+    lib.optimi_b200_clip_factor_from_norms.argtypes = [_I, _P, _I, _D, _P, _P]
     lib.optimi_b200_graph_record_begin.restype = _I
     lib.optimi_b200_graph_record_begin.argtypes = []
     lib.optimi_b200_graph_record_end.restype = _I
@@ -91,7 +94,7 @@ def _load() -> ctypes.CDLL:
 
 
 LIB = _load()
-LIB_PATH = _OVERRIDE or _build.LIB
+LIB_PATH = _build.LIB
 
 
 class peer_push:

@@ -21,16 +21,9 @@
 
 namespace optimi {
 
-#ifndef OPTIMI_THREADS
-#define OPTIMI_THREADS 128
-#endif
-constexpr int kThreads = OPTIMI_THREADS;  // threads per block
+constexpr int kThreads = 128;       // threads per block
 constexpr int kTableBytes = 29440;  // budget for the per-tensor arrays of one by-value table
 constexpr int kBuckets = 256;       // coarse index over the tile range (see locate)
-#ifndef OPTIMI_TILES_PER_BLOCK
-#define OPTIMI_TILES_PER_BLOCK 1
-#endif
-constexpr int kTilesPerBlock = OPTIMI_TILES_PER_BLOCK;  // consecutive tiles one block walks through
 
 // SMALL = true is the few-tensor form (gradient release steps one parameter per launch): a table of a
 // few hundred bytes instead of ~30 KB keeps the launch itself cheap.
@@ -81,9 +74,39 @@ template <> __device__ __forceinline__ float sqrt_rnd<__nv_bfloat16>(float x) {
   return rnd<__nv_bfloat16>(r);
 }
 
+// Correctly rounded fp32 quotient a / b of two values of a 16-bit storage type, given y = rcp_fast(b):
+// one residual correction on an approximate reciprocal.  A quotient of two significands of at most
+// 11 bits is either exactly representable in fp32 or at least 2^-36 (relative) away from every fp32
+// rounding boundary, and q = q0 + (a - b*q0)*y is within 2^-44 of a/b, so q IS the rounded quotient —
+// provided the residual does not underflow and the quotient is a normal number (|a| >= 2^-60 suffices,
+// b being at most 2^65 as a square root plus eps) and nothing overflowed on the way.  Every failure of
+// the second kind (b zero, subnormal, infinite or NaN, a infinite or NaN, a*y out of range) turns q
+// into a NaN, so one test of |a| and one of q guard the shortcut; what they turn away takes the IEEE
+// division.  Checked on the host against the double-precision quotient for all pairs of 8-bit
+// significands with a in 2^-60..2^127, b in 2^-126..2^65, and all pairs of 11-bit significands over
+// the float16 range, with the reciprocal off by -2..+2 units: no wrong result passes the guard.
+__device__ __forceinline__ float rcp_fast(float b) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(b));
+  return y;
+}
+// the IEEE division, kept out of line so that the shortcut's rare exit is a real branch and the common
+// path does not carry the division's own instruction sequence along
+static __device__ __noinline__ float div_ieee(float a, float b) { return __fdiv_rn(a, b); }
+__device__ __forceinline__ float div16(float a, float b, float y) {
+  const float q0 = __fmul_rn(a, y);
+  const float r = __fmaf_rn(-b, q0, a);
+  float q = __fmaf_rn(r, y, q0);
+  if (__builtin_expect(!(fabsf(a) >= 0x1p-60f) || q != q, 0)) q = div_ieee(a, b);
+  return q;
+}
+
 // Unpack a 16-byte vector into fp32 (exact) and pack fp32 values that are already representable in T.
 template <typename T> struct Pack;
 template <> struct Pack<float> {
+  static constexpr int EPW = 1;  // elements per 32-bit word
+  static __device__ __forceinline__ void unpack_word(uint32_t w, float (&x)[1]) { x[0] = __uint_as_float(w); }
+  static __device__ __forceinline__ uint32_t pack_word(const float (&x)[1]) { return __float_as_uint(x[0]); }
   static __device__ __forceinline__ void unpack(uint4 r, float (&x)[4]) {
     x[0] = __uint_as_float(r.x); x[1] = __uint_as_float(r.y); x[2] = __uint_as_float(r.z); x[3] = __uint_as_float(r.w);
   }
@@ -92,8 +115,18 @@ template <> struct Pack<float> {
   }
   static __device__ __forceinline__ float load1(const float* p) { return *p; }
   static __device__ __forceinline__ void store1(float* p, float x) { *p = x; }
+  static __device__ __forceinline__ void kahan2(uint32_t&, uint32_t&) {}  // no Kahan compensation in fp32 storage
 };
 template <> struct Pack<__nv_bfloat16> {
+  static constexpr int EPW = 2;
+  static __device__ __forceinline__ void unpack_word(uint32_t w, float (&x)[2]) {  // bf16 -> fp32 is a 16-bit shift
+    x[0] = __uint_as_float(w << 16);
+    x[1] = __uint_as_float(w & 0xffff0000u);
+  }
+  static __device__ __forceinline__ uint32_t pack_word(const float (&x)[2]) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(x[0], x[1]);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
   static __device__ __forceinline__ void unpack(uint4 r, float (&x)[8]) {
     const uint32_t w[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
@@ -113,8 +146,29 @@ template <> struct Pack<__nv_bfloat16> {
   }
   static __device__ __forceinline__ float load1(const __nv_bfloat16* p) { return __bfloat162float(*p); }
   static __device__ __forceinline__ void store1(__nv_bfloat16* p, float x) { *p = __float2bfloat16_rn(x); }
+  // The Kahan tail (g <- p ; p <- p + k ; g <- g - p ; k <- k + g) on two packed elements at once.  Each of the
+  // three ops takes two values of the storage type and rounds to the storage type; rounding the exact sum
+  // directly gives what the fp32 sum rounded again gives (a 24-bit intermediate is more than twice the 8 or
+  // 11 bits of the operands plus two, the condition under which double rounding of a sum is harmless), so the
+  // native packed instructions reproduce the fp32 sequence bit for bit at a quarter of the instructions.
+  static __device__ __forceinline__ void kahan2(uint32_t& p, uint32_t& k) {
+    uint32_t np, err;
+    asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(np) : "r"(p), "r"(k));
+    asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(err) : "r"(p), "r"(np));
+    asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(k) : "r"(k), "r"(err));
+    p = np;
+  }
 };
 template <> struct Pack<__half> {
+  static constexpr int EPW = 2;
+  static __device__ __forceinline__ void unpack_word(uint32_t w, float (&x)[2]) {
+    float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
+    x[0] = f.x; x[1] = f.y;
+  }
+  static __device__ __forceinline__ uint32_t pack_word(const float (&x)[2]) {
+    __half2 h = __floats2half2_rn(x[0], x[1]);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
   static __device__ __forceinline__ void unpack(uint4 r, float (&x)[8]) {
     const uint32_t w[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
@@ -134,6 +188,13 @@ template <> struct Pack<__half> {
   }
   static __device__ __forceinline__ float load1(const __half* p) { return __half2float(*p); }
   static __device__ __forceinline__ void store1(__half* p, float x) { *p = __float2half_rn(x); }
+  static __device__ __forceinline__ void kahan2(uint32_t& p, uint32_t& k) {  // see Pack<__nv_bfloat16>::kahan2
+    uint32_t np, err;
+    asm("add.rn.f16x2 %0, %1, %2;" : "=r"(np) : "r"(p), "r"(k));
+    asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(err) : "r"(p), "r"(np));
+    asm("add.rn.f16x2 %0, %1, %2;" : "=r"(k) : "r"(k), "r"(err));
+    p = np;
+  }
 };
 
 // streaming 16-byte accesses: every byte is touched once per step
@@ -161,8 +222,8 @@ struct Span {
   int len;          // elements in this tile (<= tile size)
 };
 
-// `block_elems` = elements one block covers (kTilesPerBlock tiles).  s.len is the number of elements
-// of the tensor left from s.begin, capped at block_elems.
+// `block_elems` = elements one block covers.  s.len is the number of elements of the tensor left
+// from s.begin, capped at block_elems.
 template <class Table>
 __device__ __forceinline__ Span locate(const Table& tab, int block, int block_elems) {
   int t = tab.bucket_tensor[block >> tab.bucket_shift];
@@ -177,15 +238,16 @@ __device__ __forceinline__ Span locate(const Table& tab, int block, int block_el
 
 // Fetches the block's base pointers (advanced to the tile) and reports whether every present list
 // is 16-byte aligned there; tile offsets are multiples of 16 bytes, so only the tensors' base
-// addresses decide.
+// addresses decide.  The entry of a list that is absent (NULL) is meaningless and never dereferenced:
+// an op neither reads nor writes a list the launch did not get.
 template <typename T, int NL, class Table>
 __device__ __forceinline__ bool tile_pointers(const Table& tab, const Span& s, T* (&p)[NL]) {
-  uintptr_t bits = 0;
+  uint32_t bits = 0;
 #pragma unroll
   for (int l = 0; l < NL; l++) {
     T* base = reinterpret_cast<T*>(tab.ptr[l][s.tensor]);
-    bits |= reinterpret_cast<uintptr_t>(base);
-    p[l] = base ? base + s.begin : nullptr;
+    bits |= (uint32_t)reinterpret_cast<uintptr_t>(base);
+    p[l] = base + s.begin;
   }
   return (bits & 15) == 0;
 }
@@ -204,10 +266,16 @@ struct PeerPush {
   int n;
   long long delta[kMaxPeers];
 };
+// Blocks start their round over the peers at different peers (block index modulo the peer count), so
+// that the SMs do not all store to the same peer at the same moment.
 template <typename T>
 __device__ __forceinline__ void push_vec(const PeerPush& push, T* local, uint4 v) {
-  for (int j = 0; j < push.n; j++)
+  const int n = push.n;
+  int j = (int)(blockIdx.x % (unsigned)n);
+  for (int c = 0; c < n; c++) {
     *reinterpret_cast<uint4*>(reinterpret_cast<char*>(local) + push.delta[j]) = v;
+    if (++j == n) j = 0;
+  }
 }
 template <typename T>
 __device__ __forceinline__ void push_one(const PeerPush& push, T* local, T v) {
@@ -272,7 +340,10 @@ __device__ __forceinline__ float pull_one(const PeerPull& pull, const T* local) 
 //   Ctx / context(...)        per-tile values (per-tensor scalars for StableAdamW, empty otherwise)
 //   reads(l, args)            list l is loaded        (uniform across the launch)
 //   writes(l, args)           list l is stored back   (uniform across the launch)
-//   elem<T>(e, args, ctx)     the arithmetic for ONE element; e[l] is the element of list l as fp32
+//   elem<T, TAIL>(e, args, ctx)   the arithmetic for ONE element; e[l] is the element of list l as fp32
+//   kPackedTail, kSlotP/K     16-bit storage: whole vectors call elem with TAIL = false and finish with the Kahan tail
+//                             on packed pairs of lists kSlotP (parameter) and kSlotK (compensation)
+//   kPostTail / post_tail     what remains to be done to the parameter after that tail
 //   kSumSlot                  index of an e[] slot whose values compute_vec sums up (-1: none)
 //   kMinBlocks                blocks that must fit on one SM (register cap for the compiler)
 //   kWholeTileBranch          give whole tiles their own straight-line branch (a code-generation choice
@@ -309,33 +380,57 @@ __device__ __forceinline__ void store_vec(const Vecs<Op::NL>& v, T* const (&p)[O
   }
 }
 
+__device__ __forceinline__ uint32_t& word_of(uint4& v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
+
+// One 16-byte vector per list, 32-bit word by word: the one (fp32) or two (16-bit types) elements of a
+// word are unpacked, run through the op and packed back before the next word is touched, so that few
+// values are live at a time; the packed Kahan tail then works on the word in place.
 template <typename T, class Op>
 __device__ __forceinline__ float compute_vec(Vecs<Op::NL>& v, const typename Op::Args& a, const typename Op::Ctx& ctx) {
-  constexpr int N = VecN<T>::N;
-  float x[Op::NL][N];
-#pragma unroll
-  for (int l = 0; l < Op::NL; l++) {
-    if (Op::reads(l, a)) {
-      Pack<T>::unpack(v.r[l], x[l]);
-    } else {
-#pragma unroll
-      for (int j = 0; j < N; j++) x[l][j] = 0.f;
-    }
-  }
+  constexpr int EPW = Pack<T>::EPW;  // elements per word
+  constexpr bool PACKED_TAIL = Op::kPackedTail && sizeof(T) == 2;
   float sum = 0.f;
 #pragma unroll
-  for (int j = 0; j < N; j++) {
-    float e[Op::NL];
+  for (int i = 0; i < 4; i++) {
+    float e[EPW][Op::NL];
 #pragma unroll
-    for (int l = 0; l < Op::NL; l++) e[l] = x[l][j];
-    Op::template elem<T>(e, a, ctx);
+    for (int l = 0; l < Op::NL; l++) {
+      if (Op::reads(l, a)) {
+        float x[EPW];
+        Pack<T>::unpack_word(word_of(v.r[l], i), x);
 #pragma unroll
-    for (int l = 0; l < Op::NL; l++) x[l][j] = e[l];
-    if (Op::kSumSlot >= 0) sum += e[Op::kSumSlot < 0 ? 0 : Op::kSumSlot];
+        for (int j = 0; j < EPW; j++) e[j][l] = x[j];
+      } else {
+#pragma unroll
+        for (int j = 0; j < EPW; j++) e[j][l] = 0.f;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < EPW; j++) {
+      Op::template elem<T, !PACKED_TAIL>(e[j], a, ctx);
+      if (Op::kSumSlot >= 0) sum += e[j][Op::kSumSlot < 0 ? 0 : Op::kSumSlot];
+    }
+#pragma unroll
+    for (int l = 0; l < Op::NL; l++) {
+      if (Op::writes(l, a)) {
+        float x[EPW];
+#pragma unroll
+        for (int j = 0; j < EPW; j++) x[j] = e[j][l];
+        word_of(v.r[l], i) = Pack<T>::pack_word(x);
+      }
+    }
+    if constexpr (PACKED_TAIL) {
+      uint32_t &pw = word_of(v.r[Op::kSlotP], i), &kw = word_of(v.r[Op::kSlotK], i);
+      Pack<T>::kahan2(pw, kw);
+      if constexpr (Op::kPostTail) {
+        float x[EPW];
+        Pack<T>::unpack_word(pw, x);
+#pragma unroll
+        for (int j = 0; j < EPW; j++) x[j] = Op::template post_tail<T>(x[j], a);
+        pw = Pack<T>::pack_word(x);
+      }
+    }
   }
-#pragma unroll
-  for (int l = 0; l < Op::NL; l++)
-    if (Op::writes(l, a)) v.r[l] = Pack<T>::pack(x[l]);
   return sum;
 }
 
@@ -346,7 +441,7 @@ __device__ __forceinline__ float scalar_elem(T* const (&p)[Op::NL], int i, const
 #pragma unroll
   for (int l = 0; l < Op::NL; l++) e[l] = Op::reads(l, a) ? Pack<T>::load1(p[l] + i) : 0.f;
   if constexpr (Op::kPull) e[1] = pull_one<T>(a.pull, p[1] + i);
-  Op::template elem<T>(e, a, ctx);
+  Op::template elem<T, true>(e, a, ctx);
 #pragma unroll
   for (int l = 0; l < Op::NL; l++)
     if (Op::writes(l, a)) Pack<T>::store1(p[l] + i, e[l]);
@@ -362,13 +457,13 @@ __device__ __forceinline__ double process_tile(const Table& tab, const typename 
   constexpr int V = VecN<T>::N;
   constexpr int U = Op::U;
   constexpr int TILE = kThreads * U * V;
-  s = locate(tab, blockIdx.x, TILE * kTilesPerBlock);
+  s = locate(tab, blockIdx.x, TILE);
   T* p[Op::NL];
   const bool aligned = tile_pointers<T, Op::NL, Table>(tab, s, p);
   const typename Op::Ctx ctx = Op::context(tab, s, args);
   double acc = 0.0;
   int done = 0;
-  if (Op::kWholeTileBranch && kTilesPerBlock == 1 && aligned && s.len == TILE) {
+  if (Op::kWholeTileBranch && aligned && s.len == TILE) {
     // a whole tile, as straight-line code ahead of the general loops below (same work; for some ops
     // the compiler's schedule of this form runs measurably faster, for others slower: see kWholeTileBranch)
     Vecs<Op::NL> v[U];
@@ -411,15 +506,8 @@ __device__ __forceinline__ double process_tile(const Table& tab, const typename 
 
 // Op::kMinBlocks caps the registers per thread (65536 / (kThreads * kMinBlocks)): residency, not
 // per-thread instruction-level parallelism, is what keeps the memory pipeline full here.
-// fp16 needs the IEEE square root and a two-instruction rounding, hence a slightly larger budget.
-template <typename T, class Op>
-constexpr int min_blocks() {
-  constexpr int capped = Op::kMinBlocks > 10 ? 10 : Op::kMinBlocks;
-  return sizeof(T) == 2 && !__is_same(T, __nv_bfloat16) ? (capped > 2 ? capped - 2 : 1) : Op::kMinBlocks;
-}
-
 template <typename T, class Op, bool SMALL>
-__global__ void __launch_bounds__(kThreads, min_blocks<T, Op>()) mta_kernel(const __grid_constant__ MtaTable<Op::NL, SMALL> tab,
+__global__ void __launch_bounds__(kThreads, Op::kMinBlocks) mta_kernel(const __grid_constant__ MtaTable<Op::NL, SMALL> tab,
                                                        const __grid_constant__ typename Op::Args args) {
   Span s;
   process_tile<T, Op>(tab, args, s);

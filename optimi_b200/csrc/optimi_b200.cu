@@ -202,7 +202,7 @@ static int for_each_table(int n, const int64_t* numels, void* const* const (&lis
 
 // elements one block covers
 template <typename T, class Op>
-constexpr int tile_of() { return kThreads * Op::U * VecN<T>::N * kTilesPerBlock; }
+constexpr int tile_of() { return kThreads * Op::U * VecN<T>::N; }
 
 template <typename T, class Op>
 static int launch_op(const char* name, int n, const int64_t* numels, void* const* const (&lists)[Op::NL],
@@ -243,9 +243,9 @@ OPTIMI_SHARED(thread_local PeerPull g_pull, = {0 COMMA 1.0f COMMA {0}});
 template <typename T, class Op, bool PULLABLE = true>
 static int launch_maybe_push(const char* name, int n, const int64_t* numels, void* const* const (&lists)[Op::NL],
                              const typename Op::Args& args, cudaStream_t stream) {
-  if (g_grad_factor && (g_pull.n > 0 || g_push.n > 0))
-    return fail(OPTIMI_ERR_INVALID_ARGUMENT, "%s: a gradient factor cannot be combined with the peer push / pull", name);
   if (g_pull.n > 0) {
+    if (g_grad_factor)
+      return fail(OPTIMI_ERR_INVALID_ARGUMENT, "%s: a gradient factor cannot be combined with the gradient pull", name);
     if constexpr (PULLABLE) {
       PeerArgs<typename Op::Args> pa;
       pa.base = args;
@@ -259,6 +259,16 @@ static int launch_maybe_push(const char* name, int n, const int64_t* numels, voi
     }
   }
   if (g_push.n > 0) {
+    if constexpr (PULLABLE) {
+      if (g_grad_factor) {  // scale the gradients on load, push the parameters on store
+        PeerArgs<ScaledArgs<typename Op::Args>> pa;
+        pa.base.base = args;
+        pa.base.factor = g_grad_factor;
+        pa.push = g_push;
+        pa.pull.n = 0;
+        return launch_op<T, PeerOp<ScaledOp<Op>, 0>>(name, n, numels, lists, pa, stream);
+      }
+    }
     PeerArgs<typename Op::Args> pa;
     pa.base = args;
     pa.push = g_push;
@@ -404,6 +414,35 @@ __global__ void __launch_bounds__(256) clip_factor_kernel(const float* __restric
     out[0] = factor;
     out[1] = total;
   }
+}
+
+// The same clip factor in three separable steps, for gradients whose tensors are spread over several
+// ranks or dtypes: per-tensor (or per-piece) sums of squares in double, to be added up by the caller
+// wherever the pieces of a tensor live; per-tensor norms rounded to each tensor's storage type; the
+// factor from the norms, in the storage type torch would promote the norms to.
+template <bool SMALL>
+__global__ void __launch_bounds__(256) sumsq_finalize_kernel(const __grid_constant__ MtaTable<2, SMALL> tab,
+                                                             const double* __restrict__ partial, double* __restrict__ sumsq) {
+  const int t = blockIdx.x;
+  const int c0 = tab.tile_start[t], c1 = tab.tile_start[t + 1];
+  double acc = 0.0;
+  for (int c = c0 + threadIdx.x; c < c1; c += 256) acc += partial[tab.tile_base + c];
+  __shared__ double warp_sum[8];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, o);
+  if ((threadIdx.x & 31) == 0) warp_sum[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double sum = 0.0;
+    for (int w = 0; w < 8; w++) sum += warp_sum[w];
+    sumsq[tab.tensor_base + t] = sum;
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) norms_from_sumsq_kernel(const double* __restrict__ sumsq, int n, float* __restrict__ norms) {
+  const int i = blockIdx.x * 256 + threadIdx.x;
+  if (i < n) norms[i] = rnd<T>(__fsqrt_rn((float)sumsq[i]));
 }
 
 static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
@@ -822,6 +861,74 @@ int optimi_b200_grad_clip_factor(int n, void* const* grads, const int64_t* numel
     case OPTIMI_BF16: return typed(__nv_bfloat16{});
     default: return typed(__half{});
   }
+}
+
+int optimi_b200_grad_sumsq(int n, void* const* grads, const int64_t* numels, int dtype, double* sumsq, void* workspace,
+                           size_t workspace_bytes, void* stream) {
+  const char* fn = "optimi_b200_grad_sumsq";
+  void* const* const lists[2] = {grads, nullptr};
+  const bool req[2] = {true, false};
+  static const char* const names[2] = {"grads", ""};
+  int rc = check_lists(fn, n, numels, dtype, 2, lists, req, names);
+  if (rc != OPTIMI_OK || n == 0) return rc;
+  if (!sumsq) return fail(OPTIMI_ERR_INVALID_ARGUMENT, "%s: sumsq is NULL", fn);
+  const size_t need = optimi_b200_grad_clip_workspace_bytes(n, numels) - 16;
+  if (!workspace || workspace_bytes < need)
+    return fail(OPTIMI_ERR_WORKSPACE_TOO_SMALL, "%s: workspace of %zu bytes given, %zu needed", fn,
+                workspace ? workspace_bytes : (size_t)0, need);
+  if (reinterpret_cast<uintptr_t>(workspace) & 15) return fail(OPTIMI_ERR_INVALID_ARGUMENT, "%s: workspace is not 16-byte aligned", fn);
+  double* partial = reinterpret_cast<double*>(workspace);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (g_graph.mode != kGraphUpdate) {  // tensors without elements launch nothing: their sum is zero
+    cudaError_t e = cudaMemsetAsync(sumsq, 0, (size_t)n * sizeof(double), s);
+    if (e != cudaSuccess) return fail(OPTIMI_ERR_CUDA, "%s: cudaMemsetAsync: %s", fn, cudaGetErrorString(e));
+  }
+  auto typed = [&](auto tag) {
+    using T = decltype(tag);
+    auto pass = [&](auto small) {
+      constexpr bool SMALL = decltype(small)::value;
+      return for_each_table<2, SMALL>(n, numels, lists, tile_of<T, SumSqOp>(), [&](const MtaTable<2, SMALL>& tab, int tiles) {
+        int r = launch_kernel(fn, tile_sum_kernel<T, SumSqOp, SMALL>, tiles, kThreads, s, tab, SumSqArgs{}, partial);
+        if (r != OPTIMI_OK) return r;
+        const double* partial_in = partial;
+        return launch_kernel(fn, sumsq_finalize_kernel<SMALL>, tab.n_tensors, 256, s, tab, partial_in, sumsq);
+      });
+    };
+    return n <= MtaTable<2, true>::CAP ? pass(std::true_type{}) : pass(std::false_type{});
+  };
+  switch (dtype) {
+    case OPTIMI_F32: return typed(float{});
+    case OPTIMI_BF16: return typed(__nv_bfloat16{});
+    default: return typed(__half{});
+  }
+}
+
+int optimi_b200_grad_norms_from_sumsq(int n, const double* sumsq, int dtype, float* norms, void* stream) {
+  const char* fn = "optimi_b200_grad_norms_from_sumsq";
+  if (n < 0) return fail(OPTIMI_ERR_INVALID_ARGUMENT, "%s: n_tensors=%d is negative", fn, n);
+  if (n == 0) return OPTIMI_OK;
+  if (!sumsq || !norms) return fail(OPTIMI_ERR_INVALID_ARGUMENT, "%s: sumsq or norms is NULL", fn);
+  cudaStream_t s = (cudaStream_t)stream;
+  const unsigned grid = (unsigned)((n + 255) / 256);
+  switch (dtype) {
+    case OPTIMI_F32: return launch_kernel(fn, norms_from_sumsq_kernel<float>, grid, 256, s, sumsq, n, norms);
+    case OPTIMI_BF16: return launch_kernel(fn, norms_from_sumsq_kernel<__nv_bfloat16>, grid, 256, s, sumsq, n, norms);
+    case OPTIMI_F16: return launch_kernel(fn, norms_from_sumsq_kernel<__half>, grid, 256, s, sumsq, n, norms);
+  }
+  return fail(OPTIMI_ERR_INVALID_ARGUMENT, "%s: unknown dtype code %d", fn, dtype);
+}
+
+int optimi_b200_clip_factor_from_norms(int n, const float* norms, int dtype, double max_norm, float* out, void* stream) {
+  const char* fn = "optimi_b200_clip_factor_from_norms";
+  if (n <= 0) return fail(OPTIMI_ERR_INVALID_ARGUMENT, "%s: no tensors", fn);
+  if (!norms || !out) return fail(OPTIMI_ERR_INVALID_ARGUMENT, "%s: norms or out is NULL", fn);
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (dtype) {
+    case OPTIMI_F32: return launch_kernel(fn, clip_factor_kernel<float>, 1, 256, s, norms, n, (float)max_norm, out);
+    case OPTIMI_BF16: return launch_kernel(fn, clip_factor_kernel<__nv_bfloat16>, 1, 256, s, norms, n, (float)max_norm, out);
+    case OPTIMI_F16: return launch_kernel(fn, clip_factor_kernel<__half>, 1, 256, s, norms, n, (float)max_norm, out);
+  }
+  return fail(OPTIMI_ERR_INVALID_ARGUMENT, "%s: unknown dtype code %d", fn, dtype);
 }
 
 #endif  // part 2 (continues below with the static-scratch variant)

@@ -9,22 +9,16 @@
 //
 // Template flags: KAHAN = Kahan-compensated update (16-bit storage only), UPDATE = false is the
 // optimizer-accumulation micro-step (state averages only).
+//
+// Flag of elem<T, TAIL>: TAIL = false leaves the closing Kahan tail (p += k with the error fed back
+// into k) to the caller, who does it on packed pairs (Pack<T>::kahan2) — an op offers this with
+// kPackedTail and names the slots with kSlotP / kSlotK; what must still happen to the parameter after
+// the tail goes into post_tail (kPostTail).
 #pragma once
 
 #include "mta_common.cuh"
 
 namespace optimi {
-
-// vectors per thread per stream in a full tile (tuning knobs; the defaults are the measured best)
-#ifndef OPTIMI_U_ADAM
-#define OPTIMI_U_ADAM 1
-#endif
-#ifndef OPTIMI_U_NARROW
-#define OPTIMI_U_NARROW 1
-#endif
-#ifndef OPTIMI_U_WIDE
-#define OPTIMI_U_WIDE 1
-#endif
 
 enum WdMode : int { kWdNone = 0, kWdDecoupled = 1, kWdL2 = 2 };
 
@@ -43,9 +37,17 @@ __device__ __forceinline__ float denominator(float v, float eps) {
   return rnd<T>(__fadd_rn(sqrt_rnd<T>(v), eps));
 }
 
+// correctly rounded a / b; for the 16-bit storage types through the one-correction shortcut
+template <typename T>
+__device__ __forceinline__ float quotient(float a, float b) {
+  if constexpr (sizeof(T) == 2) return div16(a, b, rcp_fast(b));
+  else return __fdiv_rn(a, b);
+}
+
 // addcdiv: x + value * (a / b)
+template <typename T>
 __device__ __forceinline__ float addcdiv_op(float x, float a, float b, float value) {
-  return __fmaf_rn(value, __fdiv_rn(a, b), x);
+  return __fmaf_rn(value, quotient<T>(a, b), x);
 }
 
 // lerp ; mul ; addcmul                                    (e.g. optimi/adam.py:431-434)
@@ -65,16 +67,17 @@ __device__ __forceinline__ void weight_decay(float& p, float& g, int mode, float
 struct OpBase {
   using Ctx = NoCtx;
   static constexpr int kSumSlot = -1;
-#ifndef OPTIMI_MIN_BLOCKS
-#define OPTIMI_MIN_BLOCKS 10
-#endif
-  static constexpr int kMinBlocks = OPTIMI_MIN_BLOCKS;  // 10: <= 51 registers per thread at 128 threads
+  static constexpr int kMinBlocks = 12;  // <= 40 registers per thread at 128 threads
   static constexpr bool kPush = false;
   static constexpr int kPull = 0;
   static constexpr bool kWholeTileBranch = false;
   static constexpr int kGradSlot = 1;  // the list that holds the gradients
+  static constexpr bool kPackedTail = false, kPostTail = false;
+  static constexpr int kSlotP = 0, kSlotK = 0;
   template <class Table, class Args>
   static __device__ __forceinline__ NoCtx context(const Table&, const Span&, const Args&) { return NoCtx{}; }
+  template <typename T, class Args>
+  static __device__ __forceinline__ float post_tail(float p, const Args&) { return p; }
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -89,11 +92,13 @@ struct AdamArgs {
 
 template <bool KAHAN, bool UPDATE>
 struct AdamOp : OpBase {
-  static constexpr int NL = 5, U = OPTIMI_U_ADAM;
+  static constexpr int NL = 5, U = 1;
+  static constexpr bool kPackedTail = KAHAN && UPDATE;
+  static constexpr int kSlotP = 0, kSlotK = 4;
   using Args = AdamArgs;
   static __device__ __forceinline__ bool reads(int l, const Args&) { return l == 0 ? UPDATE : l == 4 ? KAHAN : true; }
   static __device__ __forceinline__ bool writes(int l, const Args&) { return l == 0 ? UPDATE : l == 4 ? KAHAN : l != 1; }
-  template <typename T>
+  template <typename T, bool TAIL>
   static __device__ __forceinline__ void elem(float (&e)[NL], const Args& a, const NoCtx&) {
     float &p = e[0], &g = e[1], &m = e[2], &v = e[3], &k = e[4];
     if (UPDATE) weight_decay<T>(p, g, a.wd_mode, a.wd);
@@ -101,10 +106,10 @@ struct AdamOp : OpBase {
     if (UPDATE) {
       const float den = denominator<T>(v, a.eps);
       if (KAHAN) {
-        k = rnd<T>(addcdiv_op(k, m, den, a.neg_lr));
-        kahan_tail<T>(p, k);
+        k = rnd<T>(addcdiv_op<T>(k, m, den, a.neg_lr));
+        if (TAIL) kahan_tail<T>(p, k);
       } else {
-        p = rnd<T>(addcdiv_op(p, m, den, a.neg_lr));
+        p = rnd<T>(addcdiv_op<T>(p, m, den, a.neg_lr));
       }
     }
   }
@@ -130,18 +135,24 @@ struct PeerOp {
   static constexpr int kMinBlocks = PULL == 0 ? (Base::kMinBlocks > 2 ? Base::kMinBlocks - 2 : 1)
                                     : PULL == 2 ? (Base::kMinBlocks > 3 ? Base::kMinBlocks - 3 : 1)
                                     : PULL == 4 ? (Base::kMinBlocks > 4 ? Base::kMinBlocks - 4 : 1)
-                                                : (Base::kMinBlocks > 5 ? Base::kMinBlocks - 5 : 1);
+                                                : (Base::kMinBlocks > 6 ? Base::kMinBlocks - 6 : 1);
   static constexpr bool kPush = true;
   static constexpr int kPull = PULL;
   static constexpr bool kWholeTileBranch = false;
+  static constexpr bool kPackedTail = Base::kPackedTail, kPostTail = Base::kPostTail;
+  static constexpr int kSlotP = Base::kSlotP, kSlotK = Base::kSlotK;
   using Args = PeerArgs<typename Base::Args>;
   using Ctx = typename Base::Ctx;
   template <class Table>
   static __device__ __forceinline__ Ctx context(const Table& tab, const Span& s, const Args& a) { return Base::context(tab, s, a.base); }
   static __device__ __forceinline__ bool reads(int l, const Args& a) { return Base::reads(l, a.base); }
   static __device__ __forceinline__ bool writes(int l, const Args& a) { return Base::writes(l, a.base); }
+  template <typename T, bool TAIL>
+  static __device__ __forceinline__ void elem(float (&e)[NL], const Args& a, const Ctx& ctx) {
+    Base::template elem<T, TAIL>(e, a.base, ctx);
+  }
   template <typename T>
-  static __device__ __forceinline__ void elem(float (&e)[NL], const Args& a, const Ctx& ctx) { Base::template elem<T>(e, a.base, ctx); }
+  static __device__ __forceinline__ float post_tail(float p, const Args& a) { return Base::template post_tail<T>(p, a.base); }
 };
 
 // Any op with its gradients multiplied, as they are loaded, by one fp32 factor read from device
@@ -161,6 +172,8 @@ struct ScaledOp {
   static constexpr int kPull = 0;
   static constexpr bool kWholeTileBranch = Base::kWholeTileBranch;
   static constexpr int kGradSlot = Base::kGradSlot;
+  static constexpr bool kPackedTail = Base::kPackedTail, kPostTail = Base::kPostTail;
+  static constexpr int kSlotP = Base::kSlotP, kSlotK = Base::kSlotK;
   using Args = ScaledArgs<typename Base::Args>;
   struct Ctx {
     typename Base::Ctx base;
@@ -172,11 +185,13 @@ struct ScaledOp {
   }
   static __device__ __forceinline__ bool reads(int l, const Args& a) { return Base::reads(l, a.base); }
   static __device__ __forceinline__ bool writes(int l, const Args& a) { return Base::writes(l, a.base); }
-  template <typename T>
+  template <typename T, bool TAIL>
   static __device__ __forceinline__ void elem(float (&e)[NL], const Args& a, const Ctx& ctx) {
     e[kGradSlot] = rnd<T>(__fmul_rn(e[kGradSlot], ctx.factor));
-    Base::template elem<T>(e, a.base, ctx.base);
+    Base::template elem<T, TAIL>(e, a.base, ctx.base);
   }
+  template <typename T>
+  static __device__ __forceinline__ float post_tail(float p, const Args& a) { return Base::template post_tail<T>(p, a.base); }
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -195,7 +210,7 @@ struct SumSqOp : OpBase {
   using Args = SumSqArgs;
   static __device__ __forceinline__ bool reads(int l, const Args&) { return l == 0; }
   static __device__ __forceinline__ bool writes(int, const Args&) { return false; }
-  template <typename T>
+  template <typename T, bool TAIL>
   static __device__ __forceinline__ void elem(float (&e)[NL], const Args&, const NoCtx&) {
     e[1] = __fmul_rn(e[0], e[0]);
   }
@@ -216,27 +231,29 @@ struct RangerArgs {
 // other Ranger steps never touch the slow weights and keep Adam's register budget.
 template <bool KAHAN, bool UPDATE, bool LOOK>
 struct RangerOp : OpBase {
-  static constexpr int NL = 6, U = OPTIMI_U_ADAM;
-  // six streams: <= 64 registers; five: as Adam (RAdam then spills one register, which measured 1 % faster
-  // than nine blocks without the spill)
-  static constexpr int kMinBlocks = LOOK ? 8 : OPTIMI_MIN_BLOCKS;
+  static constexpr int NL = 6, U = 1;
+  // six streams: <= 64 registers; five: as Adam (without the packed Kahan tail a little more is live)
+  static constexpr int kMinBlocks = LOOK ? 8 : KAHAN ? OpBase::kMinBlocks : 10;
+  // a lookahead step goes on after the tail (a second compensated sum into the slow weights): it keeps the fp32 form
+  static constexpr bool kPackedTail = KAHAN && UPDATE && !LOOK;
+  static constexpr int kSlotP = 0, kSlotK = 4;
   using Args = RangerArgs;
   static __device__ __forceinline__ bool reads(int l, const Args&) {
     return l == 0 ? UPDATE : l == 4 ? KAHAN : l == 5 ? (UPDATE && LOOK) : true;
   }
   static __device__ __forceinline__ bool writes(int l, const Args& a) { return l != 1 && reads(l, a); }
-  template <typename T>
+  template <typename T, bool TAIL>
   static __device__ __forceinline__ void elem(float (&e)[NL], const Args& a, const NoCtx&) {
     float &p = e[0], &g = e[1], &m = e[2], &v = e[3], &k = e[4], &la = e[5];
     if (UPDATE) weight_decay<T>(p, g, a.wd_mode, a.wd);
     adam_moments<T>(m, v, g, a.l1, a.beta2_hat, a.beta2_comp);
     if (UPDATE) {
       float x = KAHAN ? k : p;
-      if (a.use_rect) x = rnd<T>(addcdiv_op(x, m, denominator<T>(v, a.eps), a.neg_lr));
+      if (a.use_rect) x = rnd<T>(addcdiv_op<T>(x, m, denominator<T>(v, a.eps), a.neg_lr));
       else x = rnd<T>(__fmaf_rn(a.neg_lr, m, x));
       if (KAHAN) {
         k = x;
-        kahan_tail<T>(p, k);
+        if (TAIL || LOOK) kahan_tail<T>(p, k);
         if (LOOK) {  // optimi/ranger.py:537-549
           const float diff = rnd<T>(__fsub_rn(p, la));
           k = rnd<T>(__fmaf_rn(a.alpha, diff, k));
@@ -270,12 +287,14 @@ struct LionArgs {
 
 template <bool KAHAN, bool UPDATE>
 struct LionOp : OpBase {
-  static constexpr int NL = 4, U = OPTIMI_U_NARROW;
+  static constexpr int NL = 4, U = 1;
   static constexpr bool kWholeTileBranch = true;
+  static constexpr bool kPackedTail = KAHAN && UPDATE;
+  static constexpr int kSlotP = 0, kSlotK = 3;
   using Args = LionArgs;
   static __device__ __forceinline__ bool reads(int l, const Args&) { return l == 0 ? UPDATE : l == 3 ? KAHAN : true; }
   static __device__ __forceinline__ bool writes(int l, const Args& a) { return l != 1 && reads(l, a); }
-  template <typename T>
+  template <typename T, bool TAIL>
   static __device__ __forceinline__ void elem(float (&e)[NL], const Args& a, const NoCtx&) {
     float &p = e[0], &g = e[1], &m = e[2], &k = e[3];
     float u = 0.f;
@@ -288,7 +307,7 @@ struct LionOp : OpBase {
     if (UPDATE) {
       if (KAHAN) {
         k = rnd<T>(__fmaf_rn(a.neg_lr, u, k));
-        kahan_tail<T>(p, k);
+        if (TAIL) kahan_tail<T>(p, k);
       } else {
         p = rnd<T>(__fmaf_rn(a.neg_lr, u, p));
       }
@@ -308,13 +327,15 @@ struct SgdArgs {
 
 template <bool KAHAN, bool UPDATE>
 struct SgdOp : OpBase {
-  static constexpr int NL = 4, U = OPTIMI_U_NARROW;
+  static constexpr int NL = 4, U = 1;
+  static constexpr bool kPackedTail = KAHAN && UPDATE;
+  static constexpr int kSlotP = 0, kSlotK = 3;
   using Args = SgdArgs;
   static __device__ __forceinline__ bool reads(int l, const Args& a) {
     return l == 0 ? UPDATE : l == 2 ? a.has_momentum != 0 : l == 3 ? KAHAN : true;
   }
   static __device__ __forceinline__ bool writes(int l, const Args& a) { return l != 1 && reads(l, a); }
-  template <typename T>
+  template <typename T, bool TAIL>
   static __device__ __forceinline__ void elem(float (&e)[NL], const Args& a, const NoCtx&) {
     float &p = e[0], &g = e[1], &m = e[2], &k = e[3];
     if (UPDATE) weight_decay<T>(p, g, a.wd_mode, a.wd);
@@ -331,7 +352,7 @@ struct SgdOp : OpBase {
     if (UPDATE) {
       if (KAHAN) {
         k = rnd<T>(__fmaf_rn(a.neg_lr, upd, k));
-        kahan_tail<T>(p, k);
+        if (TAIL) kahan_tail<T>(p, k);
       } else {
         p = rnd<T>(__fmaf_rn(a.neg_lr, upd, p));
       }
@@ -352,12 +373,19 @@ struct AdanArgs {
 
 template <bool KAHAN, bool UPDATE>
 struct AdanOp : OpBase {
-  static constexpr int NL = 7, U = OPTIMI_U_WIDE;
+  static constexpr int NL = 7, U = 1;
   static constexpr int kMinBlocks = 8;  // seven streams: 64 registers, the most that still compiles without spills
+  static constexpr bool kPackedTail = KAHAN && UPDATE, kPostTail = KAHAN && UPDATE;
+  static constexpr int kSlotP = 0, kSlotK = 6;
   using Args = AdanArgs;
+  // Adan-style weight decay divides the parameter after the step (optimi/adan.py:546)
+  template <typename T>
+  static __device__ __forceinline__ float post_tail(float p, const Args& a) {
+    return a.wd_mode == 2 ? rnd<T>(__fmul_rn(p, a.wd_mul)) : p;
+  }
   static __device__ __forceinline__ bool reads(int l, const Args&) { return l == 0 ? UPDATE : l == 6 ? KAHAN : true; }
   static __device__ __forceinline__ bool writes(int l, const Args& a) { return l != 1 && reads(l, a); }
-  template <typename T>
+  template <typename T, bool TAIL>
   static __device__ __forceinline__ void elem(float (&e)[NL], const Args& a, const NoCtx&) {
     float &p = e[0], &g = e[1], &m = e[2], &d = e[3], &q = e[4], &pg = e[5], &k = e[6];
     float diff = rnd<T>(__fadd_rn(pg, g));
@@ -371,15 +399,28 @@ struct AdanOp : OpBase {
     if (UPDATE) {
       const float den = denominator<T>(q, a.eps);
       if (a.wd_mode == 1) p = rnd<T>(__fmul_rn(p, a.wd_mul));
-      if (KAHAN) {
-        k = rnd<T>(addcdiv_op(k, m, den, a.neg_lr));
-        k = rnd<T>(addcdiv_op(k, d, den, a.neg_lr_beta2));
-        kahan_tail<T>(p, k);
+      // both quotients share the denominator, and with it the reciprocal of the shortcut
+      float qm, qd;
+      if constexpr (sizeof(T) == 2) {
+        const float y = rcp_fast(den);
+        qm = div16(m, den, y);
+        qd = div16(d, den, y);
       } else {
-        p = rnd<T>(addcdiv_op(p, m, den, a.neg_lr));
-        p = rnd<T>(addcdiv_op(p, d, den, a.neg_lr_beta2));
+        qm = __fdiv_rn(m, den);
+        qd = __fdiv_rn(d, den);
       }
-      if (a.wd_mode == 2) p = rnd<T>(__fmul_rn(p, a.wd_mul));
+      if (KAHAN) {
+        k = rnd<T>(__fmaf_rn(a.neg_lr, qm, k));
+        k = rnd<T>(__fmaf_rn(a.neg_lr_beta2, qd, k));
+        if (TAIL) {
+          kahan_tail<T>(p, k);
+          p = post_tail<T>(p, a);
+        }
+      } else {
+        p = rnd<T>(__fmaf_rn(a.neg_lr, qm, p));
+        p = rnd<T>(__fmaf_rn(a.neg_lr_beta2, qd, p));
+        if (a.wd_mode == 2) p = rnd<T>(__fmul_rn(p, a.wd_mul));
+      }
     }
   }
 };
@@ -397,7 +438,7 @@ constexpr int kStableMinBlocks = 12;  // both StableAdamW passes fit 40 register
 
 template <bool REDUCE>
 struct StableMomentsOp : OpBase {
-  static constexpr int NL = 4, U = OPTIMI_U_NARROW;
+  static constexpr int NL = 4, U = 1;
   static constexpr int kMinBlocks = kStableMinBlocks;
   static constexpr bool kWholeTileBranch = true;
   static constexpr int kGradSlot = 0;
@@ -405,19 +446,14 @@ struct StableMomentsOp : OpBase {
   using Args = StableMomentsArgs;
   static __device__ __forceinline__ bool reads(int l, const Args&) { return l != 3; }
   static __device__ __forceinline__ bool writes(int l, const Args&) { return l == 1 || l == 2; }
-  template <typename T>
+  template <typename T, bool TAIL>
   static __device__ __forceinline__ void elem(float (&e)[NL], const Args& a, const NoCtx&) {
     float &g = e[0], &m = e[1], &v = e[2];
     adam_moments<T>(m, v, g, a.l1, a.beta2_hat, a.beta2_comp);
     if (REDUCE) {
       const float x = fmaxf(v, a.eps_sq);  // the larger of two values of the storage type: no rounding needed
       const float gg = rnd<T>(__fmul_rn(g, g));
-      // approximate division (2 ulp for a divisor within 2^-126..2^126, which max(v, eps^2) is unless
-      // eps itself is absurd): these terms only feed the per-tensor mean, whose summation order
-      // already differs from the reference's, and this pass is issue-bound
-      float q;
-      asm("div.approx.f32 %0, %1, %2;" : "=f"(q) : "f"(gg), "f"(x));
-      e[3] = rnd<T>(q);
+      e[3] = rnd<T>(quotient<T>(gg, x));  // div (optimi/stableadamw.py:506), correctly rounded like ATen's
     }
   }
 };
@@ -434,30 +470,34 @@ struct StableUpdateArgs {
 
 template <bool KAHAN>
 struct StableUpdateOp {
-  static constexpr int NL = 4, U = OPTIMI_U_NARROW;
+  static constexpr int NL = 4, U = 1;
   static constexpr int kSumSlot = -1;
   static constexpr int kMinBlocks = kStableMinBlocks;
   static constexpr bool kPush = false;
   static constexpr int kPull = 0;
   static constexpr bool kWholeTileBranch = true;
+  static constexpr bool kPackedTail = KAHAN, kPostTail = false;
+  static constexpr int kSlotP = 0, kSlotK = 3;
   using Args = StableUpdateArgs;
   using Ctx = float2;
+  template <typename T>
+  static __device__ __forceinline__ float post_tail(float p, const Args&) { return p; }
   template <class Table>
   static __device__ __forceinline__ float2 context(const Table& tab, const Span& s, const Args& a) {
     return a.tensor_scalars[tab.tensor_base + s.tensor];
   }
   static __device__ __forceinline__ bool reads(int l, const Args&) { return l == 3 ? KAHAN : true; }
   static __device__ __forceinline__ bool writes(int l, const Args&) { return l == 0 || (l == 3 && KAHAN); }
-  template <typename T>
+  template <typename T, bool TAIL>
   static __device__ __forceinline__ void elem(float (&e)[NL], const Args& a, const float2& sc) {
     float &p = e[0], &m = e[1], &v = e[2], &k = e[3];
     if (a.has_wd) p = rnd<T>(__fmul_rn(p, sc.y));
     const float den = denominator<T>(v, a.eps);
     if (KAHAN) {
-      k = rnd<T>(addcdiv_op(k, m, den, sc.x));
-      kahan_tail<T>(p, k);
+      k = rnd<T>(addcdiv_op<T>(k, m, den, sc.x));
+      if (TAIL) kahan_tail<T>(p, k);
     } else {
-      p = rnd<T>(addcdiv_op(p, m, den, sc.x));
+      p = rnd<T>(addcdiv_op<T>(p, m, den, sc.x));
     }
   }
 };

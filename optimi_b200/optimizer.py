@@ -233,6 +233,10 @@ class OptimiOptimizer(Optimizer):
             return grad.clone()
         return (grad.float() * self._grad_factor.to(grad.device)).to(grad.dtype)  # fp32 product, one rounding: the kernels' arithmetic
 
+    def _state_needs_first_gradient(self, group: dict[str, Any]) -> bool:
+        """Whether `_new_state` reads the parameter's first gradient (Adan, SGD with `torch_init`)."""
+        return False
+
     def _kahan_state(self, group: dict[str, Any], param: Tensor) -> Tensor | None:
         """Kahan compensation buffer: on by default for bf16/fp16 parameters (`kahan_sum=None`),
         never for float32 (e.g. optimi/adam.py:100-106)."""
@@ -310,8 +314,8 @@ class OptimiOptimizer(Optimizer):
         on the device (one read of the gradients, PyTorch's own order of roundings), and makes the
         NEXT `step()` scale the gradients by the coefficient as it loads them.  Returns the total norm
         as a 0-dim CUDA tensor (no host synchronisation).  Saves the read-modify-write pass over the
-        gradients that clipping in place costs.  All gradients must share one device and dtype; not
-        for gradient release, where parameters are stepped before all gradients exist."""
+        gradients that clipping in place costs.  All gradients must live on one device; not for gradient
+        release, where parameters are stepped before all gradients exist."""
         if self.defaults.get("gradient_release", False):
             raise RuntimeError("clip_grad_norm needs all gradients before any parameter is stepped: not with gradient_release")
         grads = [p.grad for group in self.param_groups for p in group["params"] if p.grad is not None]
@@ -320,9 +324,15 @@ class OptimiOptimizer(Optimizer):
         g0 = grads[0]
         if not g0.is_cuda or g0.dtype not in _lib.DTYPE_CODE:
             raise RuntimeError("clip_grad_norm: gradients must be CUDA float32, bfloat16 or float16 tensors")
+        if any(g.dtype != g0.dtype for g in grads):
+            # several dtypes (float32 embeddings beside a bfloat16 body): per-dtype passes, norms combined in float32
+            if torch.cuda.is_current_stream_capturing():
+                raise NotImplementedError("clip_grad_norm over several dtypes cannot be captured into a CUDA graph")
+            with_grad = [p for group in self.param_groups for p in group["params"] if p.grad is not None]
+            return self._clip_from_sumsq(with_grad, list(range(len(with_grad))), [p.grad.dtype for p in with_grad], max_norm)
         for g in grads:
-            if g.device != g0.device or g.dtype != g0.dtype:
-                raise NotImplementedError("clip_grad_norm: all gradients must share one device and dtype")
+            if g.device != g0.device:
+                raise NotImplementedError("clip_grad_norm: all gradients must live on one device")
             if not g.is_contiguous() and not torch._prims_common.is_non_overlapping_and_dense(g):
                 raise RuntimeError("clip_grad_norm: gradients must be dense")
         if self._clip_out is None or self._clip_out.device != g0.device:
@@ -347,6 +357,67 @@ class OptimiOptimizer(Optimizer):
         _lib.check(rc)
         self._grad_factor, self._grad_factor_once = self._clip_out[:1], not capturing
         return self._clip_out[1].clone()  # the two-float buffer is reused by the next call
+
+    @torch.no_grad()
+    def _clip_from_sumsq(self, tensors: list[Tensor], owners: list[int], dtypes: list[torch.dtype], max_norm: float,
+                         reduce_sums: Callable[[Tensor], None] | None = None) -> Tensor:  # fmt: skip
+        """The clip coefficient in separable steps (the general form behind `clip_grad_norm`): `tensors` are
+        parameters, or pieces of parameters, whose `.grad` is read; `owners[i]` is the index of the whole
+        tensor that piece i belongs to and `dtypes[j]` the dtype of whole tensor j.  Per-piece sums of squares
+        (double) are added into per-tensor sums, `reduce_sums` (if given) adds the other ranks' contributions
+        in place, each tensor's norm is rounded to its own dtype as `torch._foreach_norm` would return it, and
+        the coefficient is computed in the dtype PyTorch promotes the stacked norms to (the common dtype, or
+        float32 when they differ).  Arms the next `step()` with the coefficient; returns the total norm."""
+        device = None
+        for t in tensors:
+            if t.grad is not None:
+                device = t.grad.device
+                break
+        if device is None:
+            device = tensors[0].device if tensors else torch.device("cuda", torch.cuda.current_device())
+        n_full = len(dtypes)
+        sumsq = torch.zeros(n_full, dtype=torch.float64, device=device)
+        stream_ptr = torch._C._cuda_getCurrentRawStream(device.index)
+        by_dtype: dict[torch.dtype, list[int]] = {}
+        for i, t in enumerate(tensors):
+            if t.grad is None:
+                continue
+            g = t.grad
+            if not g.is_cuda or g.dtype not in _lib.DTYPE_CODE or g.device != device:
+                raise RuntimeError("clip_grad_norm: gradients must be CUDA float32, bfloat16 or float16 tensors on one device")
+            if not g.is_contiguous() and not torch._prims_common.is_non_overlapping_and_dense(g):
+                raise RuntimeError("clip_grad_norm: gradients must be dense")
+            by_dtype.setdefault(g.dtype, []).append(i)
+        with torch.cuda.device(device):
+            for dtype, idx in by_dtype.items():
+                grads = [tensors[i].grad for i in idx]
+                numels = _lib.numel_array(grads)
+                numels_arg = ctypes.cast(numels, ctypes.c_void_p)
+                need = _lib.LIB.optimi_b200_grad_clip_workspace_bytes(len(grads), numels_arg)
+                ws = F._stable_workspace(device, stream_ptr, need)
+                piece = torch.empty(len(grads), dtype=torch.float64, device=device)
+                ptrs = _lib.PointerArray(grads)
+                _lib.check(_lib.LIB.optimi_b200_grad_sumsq(len(grads), ptrs.ptr, numels_arg, _lib.DTYPE_CODE[dtype], piece.data_ptr(),
+                                                          ws.data_ptr(), ws.numel(), stream_ptr))  # fmt: skip
+                # a whole tensor has at most one piece in `tensors`, so this is a plain scatter
+                sumsq[torch.tensor([owners[i] for i in idx], device=device)] = piece
+            if reduce_sums is not None:
+                reduce_sums(sumsq)
+            norms = torch.zeros(n_full, dtype=torch.float32, device=device)
+            kinds = sorted(set(dtypes), key=str)
+            for dtype in kinds:
+                sel = torch.tensor([j for j, d in enumerate(dtypes) if d == dtype], device=device)
+                sub = sumsq[sel].contiguous()
+                out = torch.empty(sub.numel(), dtype=torch.float32, device=device)
+                _lib.check(_lib.LIB.optimi_b200_grad_norms_from_sumsq(sub.numel(), sub.data_ptr(), _lib.DTYPE_CODE[dtype], out.data_ptr(), stream_ptr))
+                norms[sel] = out
+            total_dtype = kinds[0] if len(kinds) == 1 else torch.float32
+            if self._clip_out is None or self._clip_out.device != device:
+                self._clip_out = torch.zeros(2, dtype=torch.float32, device=device)
+            _lib.check(_lib.LIB.optimi_b200_clip_factor_from_norms(n_full, norms.data_ptr(), _lib.DTYPE_CODE[total_dtype], float(max_norm),
+                                                                   self._clip_out.data_ptr(), stream_ptr))  # fmt: skip
+        self._grad_factor, self._grad_factor_once = self._clip_out[:1], True
+        return self._clip_out[1].clone()
 
     # ---- the step inside a CUDA graph -----------------------------------------------------------
     def _capture_step(self) -> None:
@@ -728,6 +799,9 @@ class SGD(OptimiOptimizer):
             triton=triton, gradient_release=gradient_release,
         ))  # fmt: skip
 
+    def _state_needs_first_gradient(self, group):
+        return bool(group["dampening"] and group["torch_init"])
+
     def _new_state(self, group, state, param):
         if group["dampening"] and group["torch_init"]:
             # torch.optim.SGD seeds the buffer with the gradient after L2 decay (optimi/sgd.py:101-105)
@@ -812,6 +886,9 @@ class Adan(OptimiOptimizer):
             decouple_lr=decouple_lr, max_lr=max_lr, adam_wd=adam_wd, kahan_sum=kahan_sum, foreach=foreach, triton=triton,
             gradient_release=gradient_release,
         ))  # fmt: skip
+
+    def _state_needs_first_gradient(self, group):
+        return True
 
     def _new_state(self, group, state, param):
         state["exp_avg"] = torch.zeros_like(param, memory_format=torch.preserve_format)

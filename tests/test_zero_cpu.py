@@ -160,3 +160,107 @@ def test_consolidated_state_dict_round_trip():
     assert same_layout, "consolidated state dict has another layout than the unsharded optimizer's"
     assert same_values, "consolidated state differs from the unsharded optimizer's"
     assert cont, "runs continued from the consolidated checkpoint diverge"
+
+
+def _mismatch_worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        # rank 1 was handed a model with one layer of another width: a host-made fault
+        shapes = [(33, 65), (129,), (1024, 3)] if rank == 0 else [(33, 65), (130,), (1024, 3)]
+        params = [torch.nn.Parameter(torch.zeros(s)) for s in shapes]
+        before = [p.data_ptr() for p in params]
+        try:
+            ShardedOptimizer(torch.optim.AdamW, params, lr=1e-2)
+            verdict = "no error"
+        except RuntimeError as exc:
+            verdict = str(exc)
+        untouched = before == [p.data_ptr() for p in params]  # nothing was re-pointed into a flat buffer
+        out.put((rank, verdict, untouched))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_ranks_with_different_parameter_lists_are_refused_before_anything_is_built():
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_mismatch_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = sorted(out.get(timeout=120) for _ in range(2))
+    for p in procs:
+        p.join(60)
+        assert p.exitcode == 0
+    for rank, verdict, untouched in got:
+        assert "different parameter lists" in verdict, f"rank {rank}: {verdict}"
+        assert untouched, f"rank {rank}: parameters were moved although the ranks disagree"
+
+
+def _groups_worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        g = torch.Generator().manual_seed(0)
+        shapes = [(33, 65), (129,), (1024, 3), (7,), (2000,)]
+        dtypes = [torch.float32, torch.float32, torch.float64, torch.float32, torch.float64]
+        init = [torch.randn(s, generator=g).to(d) for s, d in zip(shapes, dtypes)]
+
+        def groups(ps):  # two groups with their own options, two dtypes running across both
+            return [{"params": [ps[1], ps[3]], "weight_decay": 0.0}, {"params": [ps[0], ps[2], ps[4]], "weight_decay": 0.1, "lr": 3e-2}]
+
+        params = [torch.nn.Parameter(t.clone()) for t in init]
+        ref = [torch.nn.Parameter(t.clone()) for t in init]
+        sharded = ShardedOptimizer(torch.optim.AdamW, groups(params), lr=1e-2)
+        plain = torch.optim.AdamW(groups(ref), lr=1e-2)
+        assert len(sharded.buckets) == 2 and len(sharded.param_groups) == 2
+        assert sharded.param_groups[1]["lr"] == 3e-2 and sharded.param_groups[0]["weight_decay"] == 0.0
+        for step in range(4):
+            for p, r in zip(params, ref):
+                gr = torch.randn(p.shape, generator=g).to(p.dtype)
+                p.grad, r.grad = gr.clone(), gr.clone()
+            sharded.step()
+            plain.step()
+        same = all(torch.equal(p.detach(), r.detach()) for p, r in zip(params, ref))
+        full, want = sharded.consolidated_state_dict(), plain.state_dict()
+        layout = [g_["params"] for g_ in full["param_groups"]] == [g_["params"] for g_ in want["param_groups"]]
+        values = all(
+            torch.equal(torch.as_tensor(full["state"][i][k]).cpu(), torch.as_tensor(want["state"][i][k]).cpu())
+            for i in want["state"] for k in want["state"][i]
+        )
+        # and back into a fresh sharded optimizer, which then continues like the plain one
+        params2 = [torch.nn.Parameter(p.detach().clone()) for p in params]
+        sharded2 = ShardedOptimizer(torch.optim.AdamW, groups(params2), lr=1e-2)
+        sharded2.load_consolidated_state_dict(full)
+        for p, r in zip(params2, ref):
+            gr = torch.randn(p.shape, generator=g).to(p.dtype)
+            p.grad, r.grad = gr.clone(), gr.clone()
+        sharded2.step()
+        plain.step()
+        cont = all(torch.equal(p.detach(), r.detach()) for p, r in zip(params2, ref))
+        identical = sharded2.check_replicas()["ranks_identical"]
+        if rank == 0:
+            out.put((same, layout, values, cont, identical))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_param_groups_and_mixed_dtypes_match_unsharded():
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_groups_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    try:
+        same, layout, values, cont, identical = out.get(timeout=120)
+    finally:
+        for p in procs:
+            p.join(60)
+            if p.is_alive():
+                p.terminate()
+    assert same, "sharded parameters differ from the unsharded run"
+    assert layout, "consolidated param_groups number the parameters differently from the unsharded optimizer"
+    assert values, "consolidated state differs from the unsharded optimizer's"
+    assert cont, "the run continued from the consolidated checkpoint diverges"
+    assert identical, "check_replicas() reports differing ranks"
