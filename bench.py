@@ -16,6 +16,10 @@ Keys beyond the driver's contract:
   e2e           the same metric through the public API with gradients arriving from pinned host
                 memory every step and a small device-to-host read of the result
   step_ms / gather_ms   device time of the local step and of the all-gather (N > 1)
+  exchange_check        N > 1: after the warm-up steps every rank checksums its whole parameter buffers and the ranks
+                        compare; the run exits non-zero when they differ
+  local_step_ms         N > 1: the rank's step alone (no exchange), i.e. the per-rank step time
+  reference_gpu         N = 1: the reference's own CUDA back ends (foreach, Triton) and this build on the 1.1 B list
 """
 
 from __future__ import annotations
@@ -38,9 +42,9 @@ METRIC = "AdamW bf16-Kahan step: Gparams/s & HBM GB/s vs 8 TB/s, 8B shapes, 1/2/
 UNIT = "Gparams/s"
 BYTES_PER_PARAM = 18  # read p,g,m,v,k (10 B) + write p,m,v,k (8 B), bf16 + Kahan
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum per parameter of the bf16+Kahan kernels, from the ncu captures of the
-# 336 M-parameter case summarised in profiles/*_llama-0.3b_ncu_full.md (StableAdamW: both passes together); traffic is
-# proportional to the parameter count, so a step's traffic is this figure times its elements
+# dram__bytes_read.sum + dram__bytes_write.sum per parameter of the bf16+Kahan kernels, from ncu captures of a
+# 336 M-parameter list (StableAdamW: both passes together); traffic is proportional to the parameter count, so a
+# step's traffic is this figure times its elements
 NCU_DRAM_BYTES_PER_PARAM = {"adamw": 17.83, "adam": 17.83, "lion": 13.83, "adan": 25.83, "stableadamw": 21.72}
 
 HYPER = dict(lr=3e-4, betas=(0.9, 0.99), weight_decay=1e-5, eps=1e-6, decouple_lr=True)
@@ -95,8 +99,13 @@ def make_config(workload: str, n_gpus: int, exchange: str = "auto", optimizer: s
     """The `config` object of the JSON line; identical for both arms of one (workload, N)."""
     shapes = WORKLOADS[workload]()
     n_params = sum(numel(s) for s in shapes)
+    sample = cpu_sample_shapes(workload)
     return {
-        "workload": f"{OPTIMIZERS[optimizer][0]} bf16+Kahan, {workload} parameter shapes ({n_params} params, {len(shapes)} tensors)",
+        # the same text in both arms; it also says what the CPU reference arm, which cannot step the whole list within
+        # minutes, times per step (its ms_per_step is that sample's, its value the sample's parameters per second)
+        "workload": f"{OPTIMIZERS[optimizer][0]} bf16+Kahan, {workload} parameter shapes ({n_params} params, {len(shapes)} tensors); "
+                    f"the CPU reference arm times a bounded sample per step: the first decoder layer, {len(sample)} tensors, "
+                    f"{sum(numel(x) for x in sample)} params",
         "optimizer": OPTIMIZERS[optimizer][0], "hyper": {k: (list(v) if isinstance(v, tuple) else v) for k, v in OPTIMIZERS[optimizer][1].items()},
         "sharding": "none" if n_gpus == 1 else f"ZeRO-1 over {n_gpus} ranks, exchange={exchange} "
                     "(push: step kernel stores updated params into the peers over NVLink; nccl: all-gather after the step)",
@@ -280,11 +289,12 @@ def run_reference_arm(args):
     if rank != 0:
         return
     value, kind, cores, sample, ms, done = time_cpu_reference(args.workload, args.steps, args.warmup, budget_s=150.0, optimizer=args.optimizer)
+    config = make_config(args.workload, args.gpus, args.exchange, args.optimizer)
     line = {
         "impl": "reference", "metric": metric_name(args.optimizer), "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": done,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
-        "config": make_config(args.workload, args.gpus, args.exchange, args.optimizer),
+        "config": config,
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -295,6 +305,55 @@ def run_reference_arm(args):
 # ------------------------------------------------------------------------------------------------
 # the optimi_b200 arm
 # ------------------------------------------------------------------------------------------------
+def make_reduce_probe(sharded, params, opt_cls, opt_kw, world):
+    """--reduce-grads: an unsharded twin of ONE tensor that straddles a shard boundary, stepped on the mean of all
+    ranks' gradients (fp32 sum in rank order, times 1/world, one rounding: the fused kernel's arithmetic) beside
+    the sharded warm-up steps; the two must stay bit-identical."""
+    import torch.distributed as dist
+
+    b = sharded.buckets[0]
+    layout = b["layout"]
+    cut = layout.bounds[1]
+    pick = next((i for i, (off, n) in enumerate(zip(layout.offsets, layout.numels)) if off < cut < off + n), 0)
+    p = b["params"][pick]
+    gathered = [torch.empty_like(p.grad) for _ in range(world)]
+    dist.all_gather(gathered, p.grad.contiguous())
+    acc = gathered[0].float()
+    for g in gathered[1:]:
+        acc += g.float()
+    twin = p.detach().clone().requires_grad_(True)
+    twin.grad = (acc * (1.0 / world)).to(p.dtype)
+    del gathered, acc
+    return {"opt": opt_cls([twin], **opt_kw), "twin": twin, "sharded_tensor": p,
+            "describe": f"tensor {pick} {tuple(p.shape)}, cut by the boundary between ranks 0 and 1"}  # fmt: skip
+
+
+def measure_peer_copy_gbs(nbytes=1 << 30, repeats=5):
+    """GB/s of a plain device-to-device copy from GPU 0 to GPU 1 (two ordinary allocations, one per device, the
+    runtime's peer copy; best of `repeats`): the per-direction NVLink rate the exchange is held against."""
+    if torch.cuda.device_count() < 2:
+        return None
+    try:
+        src = torch.empty(nbytes, dtype=torch.uint8, device="cuda:0")
+        dst = torch.empty(nbytes, dtype=torch.uint8, device="cuda:1")
+        dst.copy_(src)
+        torch.cuda.synchronize("cuda:0")
+        torch.cuda.synchronize("cuda:1")
+        best = float("inf")
+        for _ in range(repeats):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            with torch.cuda.device(0):
+                e0.record()
+                dst.copy_(src, non_blocking=True)
+                e1.record()
+                e1.synchronize()
+            best = min(best, e0.elapsed_time(e1))
+        del src, dst
+        return nbytes / (best * 1e-3) / 1e9
+    except RuntimeError:
+        return None
+
+
 def run_b200_arm(args):
     import optimi_b200
     from optimi_b200 import _lib
@@ -354,9 +413,25 @@ def run_b200_arm(args):
         t.grad = g
 
     # ---- kernel-resident timing ---------------------------------------------------------------
+    probe = make_reduce_probe(sharded, params, opt_cls, opt_kw, world) if (sharded is not None and args.reduce_grads) else None
     for _ in range(max(args.warmup, 3)):
         step_resident()
+        if probe is not None:
+            probe["opt"].step()
     barrier(world)
+    # outside the timed region: do all ranks hold the same bits after the sharded warm-up steps?
+    exchange_check = None
+    if sharded is not None:
+        exchange_check = sharded.check_replicas()
+        if probe is not None:
+            exchange_check["matches_unsharded_on_mean_gradient"] = bool(torch.equal(probe["sharded_tensor"].detach(), probe["twin"].detach()))
+            exchange_check["probe_tensor"] = probe["describe"]
+            del probe
+        ok = exchange_check["ranks_identical"] and exchange_check.get("matches_unsharded_on_mean_gradient", True)
+        if not ok:
+            if rank == 0:
+                print(json.dumps({"error": "sharded step left the ranks with different parameters", "exchange_check": exchange_check}))
+            raise SystemExit(3)
     stream = torch.cuda.current_stream(device)
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
     launches0 = _lib.LIB.optimi_b200_launch_count()
@@ -392,6 +467,22 @@ def run_b200_arm(args):
     ms_per_step = total_ms / args.steps
     value = n_params / (ms_per_step * 1e-3) / 1e9
 
+    # ---- N > 1: the rank's step alone, without the exchange (the per-rank step time) ----------------
+    local_step_ms = None
+    if sharded is not None and not args.reduce_grads:
+        k_local = max(3, min(args.steps, 10))
+        sharded.step_local(dev_grads, exchange=False)
+        barrier(world)
+        l0, l1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        l0.record(stream)
+        for _ in range(k_local):
+            sharded.step_local(dev_grads, exchange=False)
+        l1.record(stream)
+        barrier(world)
+        local_step_ms = max_over_ranks(l0.elapsed_time(l1) / k_local, world, device)
+        sharded.gather_params(force=True)  # the ranks' copies diverged during the local-only steps: bring them together again
+        barrier(world)
+
     # ---- end to end: gradients from pinned host memory, result read back -----------------------
     if args.reduce_grads:
         dev_grads = [p.grad for p in params]  # end to end: each rank's full gradients arrive from the host
@@ -403,12 +494,47 @@ def run_b200_arm(args):
     h2d_bytes = sum(h.numel() * h.element_size() for h in host_grads)
     d2h_bytes = result_host.numel() * result_host.element_size()
 
-    def step_e2e():
-        for h, g in zip(host_grads, dev_grads):
-            g.copy_(h, non_blocking=True)
-        step_resident()
-        result_host.copy_(result_src.detach(), non_blocking=True)
-        torch.cuda.current_stream(device).synchronize()
+    e2e_overlap = None
+    if sharded is None:
+        # one GPU: the gradients arrive in chunks on a copy stream and every chunk is stepped as soon as it has
+        # landed (OptimiOptimizer.step_groups over one param group per chunk), so that only the last chunk's step
+        # is not hidden behind the PCIe transfer.  A fresh optimizer over the same parameters, grouped by chunk.
+        n_chunks = 16
+        del opt
+        torch.cuda.empty_cache()
+        order, acc, chunk_of, target = list(range(len(params))), 0, [], n_params / n_chunks
+        for i in order:
+            chunk_of.append(min(n_chunks - 1, int(acc / target)))
+            acc += params[i].numel()
+        chunks = [[i for i in order if chunk_of[i] == c] for c in range(n_chunks)]
+        chunks = [c for c in chunks if c]
+        opt = opt_cls([{"params": [params[i] for i in c]} for c in chunks], **opt_kw)
+        copy_stream = torch.cuda.Stream(device)
+        landed = [torch.cuda.Event() for _ in chunks]
+        e2e_overlap = {"chunks": len(chunks), "how": "gradient chunks copied on a side stream, each stepped (step_groups) when its copy has landed"}
+
+        def step_e2e():
+            main = torch.cuda.current_stream(device)
+            copy_stream.wait_stream(main)
+            with torch.cuda.stream(copy_stream):
+                for ci, c in enumerate(chunks):
+                    for i in c:
+                        dev_grads[i].copy_(host_grads[i], non_blocking=True)
+                    landed[ci].record(copy_stream)
+            for ci in range(len(chunks)):
+                main.wait_event(landed[ci])
+                opt.step_groups([ci])
+            result_host.copy_(result_src.detach(), non_blocking=True)
+            main.synchronize()
+
+    else:
+
+        def step_e2e():
+            for h, g in zip(host_grads, dev_grads):
+                g.copy_(h, non_blocking=True)
+            step_resident()
+            result_host.copy_(result_src.detach(), non_blocking=True)
+            torch.cuda.current_stream(device).synchronize()
 
     e2e_steps = max(2, min(args.steps, 5))
     step_e2e()
@@ -431,7 +557,10 @@ def run_b200_arm(args):
     else:
         peak, peak_kind = FALLBACK_HBM_GBS, "fallback"
     kernel_launches_per_step = max(1, launches // args.steps)
-    achieved = bytes_per_param * n_local / (step_ms_max * 1e-3) / 1e9
+    # the kernel against HBM: at N > 1 with the push exchange `step_ms` is NVLink-bound (it contains the exchange), so the
+    # roofline of the step kernel is taken from the local-only steps timed above
+    kernel_ms = local_step_ms if local_step_ms is not None else step_ms_max
+    achieved = bytes_per_param * n_local / (kernel_ms * 1e-3) / 1e9
     ncu_bpp = NCU_DRAM_BYTES_PER_PARAM.get(args.optimizer)
     traffic = ncu_bpp * n_local / kernel_launches_per_step if ncu_bpp is not None else None
     roofline = {
@@ -441,23 +570,54 @@ def run_b200_arm(args):
         "peak_kind": f"of {peak_kind}", "frac_of_8TBs": achieved / 8000.0, "kernel": kernel_name,
         "algorithmic_bytes_per_launch": bytes_per_param * n_local / kernel_launches_per_step,
         "algorithmic_bytes_per_param": bytes_per_param,
-        "launches_per_step": kernel_launches_per_step,
+        "launches_per_step": kernel_launches_per_step, "kernel_ms": kernel_ms,
+        "timed_as": "local-only steps (no exchange) after the timed region" if local_step_ms is not None else "the timed steps",
     }  # fmt: skip
 
     nvlink = None
-    if sharded is not None and sharded.exchange == "push":
-        # bytes this rank's step kernel stores into its peers, against the measured peer-copy rate of this pool
-        pushed = 2.0 * n_local * (world - 1)
+    if sharded is not None:
+        # what must cross NVLink per rank and step, against a peer copy measured in this very run (GPU 0 -> GPU 1,
+        # 1 GiB, best of 5); the nominal 900 GB/s per direction stands in when it cannot be measured
+        link_gbs = measure_peer_copy_gbs()
+        link_kind = "measured in this run" if link_gbs is not None else "nominal"
+        link_gbs = link_gbs or 900.0
+        pushed = 2.0 * n_local * (world - 1)  # bytes this rank's updated parameters occupy on its peers
         # with --reduce-grads the same link direction also carries the responses to the peers' gradient reads
         pulled = pushed if args.reduce_grads else 0.0
-        nvlink = {"achieved": (pushed + pulled) / (step_ms_max * 1e-3) / 1e9, "peak": 770.0, "unit": "GB/s per direction per GPU",
-                  "frac": (pushed + pulled) / (step_ms_max * 1e-3) / 1e9 / 770.0, "bytes_pushed_per_rank_per_step": pushed,
-                  "bytes_pulled_per_rank_per_step": pulled}
+        exchange_ms = step_ms_max if sharded.exchange == "push" else gather_ms_max
+        nvlink = {"achieved": (pushed + pulled) / (exchange_ms * 1e-3) / 1e9, "peak": link_gbs, "peak_kind": link_kind,
+                  "unit": "GB/s per direction per GPU", "frac": (pushed + pulled) / (exchange_ms * 1e-3) / 1e9 / link_gbs,
+                  "bytes_pushed_per_rank_per_step": pushed, "bytes_pulled_per_rank_per_step": pulled,
+                  "exchange_bound_ms": (pushed + pulled) / (link_gbs * 1e9) * 1e3,
+                  "timed_over": "the fused step kernel" if sharded.exchange == "push" else "the all-gather"}
 
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
         v, kind, cores, sample, _, _ = time_cpu_reference(args.workload, 12, 2, budget_s=20.0, optimizer=args.optimizer)
         cpu = {"value": v, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample}
+
+    # per-rank step time against the one-GPU step: t1 / (N * tN), t1 taken from a one-GPU run of the same workload on this
+    # machine if one left its record (the scaling series runs N = 1 first), else from this run's own HBM rate
+    t1_path = os.path.join("/tmp", f"optimi_b200_bench_t1_{args.workload}_{args.optimizer}.json")
+    local_eff = None
+    if world == 1:
+        try:
+            with open(t1_path, "w") as fh:
+                json.dump({"step_ms": step_ms_max, "when": time.time()}, fh)
+        except OSError:
+            pass
+    elif local_step_ms is not None:
+        try:
+            with open(t1_path) as fh:
+                rec = json.load(fh)
+            if time.time() - rec["when"] < 6 * 3600:
+                local_eff = {"value": rec["step_ms"] / (world * local_step_ms), "t1_ms": rec["step_ms"], "t1_from": "one-GPU run on this machine"}
+        except (OSError, ValueError, KeyError):
+            pass
+    bound = None
+    if sharded is not None:
+        bound = ("nvlink: the step kernel also stores every updated parameter into the peers" if sharded.exchange == "push"
+                 else "nvlink: the all-gather after the step")
 
     line = {
         "metric": metric_name(args.optimizer), "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
@@ -467,9 +627,10 @@ def run_b200_arm(args):
         "exchange": None if sharded is None else sharded.exchange, "reduce_grads": bool(args.reduce_grads),
         "hbm_gbs": achieved, "step_ms": step_ms_max, "gather_ms": gather_ms_max, "wall_ms_per_step": t_wall * 1e3 / args.steps,
         "step_ms_spread_rank0": spread,
+        "exchange_check": exchange_check, "local_step_ms": local_step_ms, "local_step_efficiency": local_eff, "bound": bound,
         "roofline": roofline, "nvlink": nvlink, "cpu_baseline": cpu,
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
-                "ms_per_step": e2e_s * 1e3, "steps": e2e_steps},
+                "ms_per_step": e2e_s * 1e3, "steps": e2e_steps, "overlap": e2e_overlap},
         "gpu_launches": int(launches), "clocks": clocks.result, "library": os.path.relpath(_lib.LIB_PATH, ROOT),
     }  # fmt: skip
     print(json.dumps(line))

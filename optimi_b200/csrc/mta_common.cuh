@@ -81,23 +81,24 @@ template <> __device__ __forceinline__ float sqrt_rnd<__nv_bfloat16>(float x) {
 // provided the residual does not underflow and the quotient is a normal number (|a| >= 2^-60 suffices,
 // b being at most 2^65 as a square root plus eps) and nothing overflowed on the way.  Every failure of
 // the second kind (b zero, subnormal, infinite or NaN, a infinite or NaN, a*y out of range) turns q
-// into a NaN, so one test of |a| and one of q guard the shortcut; what they turn away takes the IEEE
-// division.  Checked on the host against the double-precision quotient for all pairs of 8-bit
-// significands with a in 2^-60..2^127, b in 2^-126..2^65, and all pairs of 11-bit significands over
-// the float16 range, with the reciprocal off by -2..+2 units: no wrong result passes the guard.
+// into a NaN, so one test of |a| and one of q guard the shortcut.  What they turn away is rare and goes
+// one of two ways: a zero numerator is answered by q0 = a*y itself (a zero of the right sign for any
+// finite positive b, a NaN for b = 0, as the IEEE quotient), everything else by the IEEE division, kept
+// out of line so that the common path does not carry its instruction sequence along.  Checked on the
+// host against the double-precision quotient for all pairs of 8-bit significands with a in
+// 2^-60..2^127, b in 2^-126..2^65, and all pairs of 11-bit significands over the float16 range, with
+// the reciprocal off by -2..+2 units: no wrong result passes the guard.
 __device__ __forceinline__ float rcp_fast(float b) {
   float y;
   asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(b));
   return y;
 }
-// the IEEE division, kept out of line so that the shortcut's rare exit is a real branch and the common
-// path does not carry the division's own instruction sequence along
 static __device__ __noinline__ float div_ieee(float a, float b) { return __fdiv_rn(a, b); }
 __device__ __forceinline__ float div16(float a, float b, float y) {
   const float q0 = __fmul_rn(a, y);
   const float r = __fmaf_rn(-b, q0, a);
   float q = __fmaf_rn(r, y, q0);
-  if (__builtin_expect(!(fabsf(a) >= 0x1p-60f) || q != q, 0)) q = div_ieee(a, b);
+  if (__builtin_expect(!(fabsf(a) >= 0x1p-60f) || q != q, 0)) q = a == 0.f ? q0 : div_ieee(a, b);
   return q;
 }
 
@@ -340,7 +341,8 @@ __device__ __forceinline__ float pull_one(const PeerPull& pull, const T* local) 
 //   Ctx / context(...)        per-tile values (per-tensor scalars for StableAdamW, empty otherwise)
 //   reads(l, args)            list l is loaded        (uniform across the launch)
 //   writes(l, args)           list l is stored back   (uniform across the launch)
-//   elem<T, TAIL>(e, args, ctx)   the arithmetic for ONE element; e[l] is the element of list l as fp32
+//   elem<T, TAIL, L2>(e, args, ctx)   the arithmetic for ONE element; e[l] is the element of list l as fp32
+//   kHasL2 / l2(args)         the op has an L2 weight-decay form, and whether this launch is one
 //   kPackedTail, kSlotP/K     16-bit storage: whole vectors call elem with TAIL = false and finish with the Kahan tail
 //                             on packed pairs of lists kSlotP (parameter) and kSlotK (compensation)
 //   kPostTail / post_tail     what remains to be done to the parameter after that tail
@@ -385,8 +387,8 @@ __device__ __forceinline__ uint32_t& word_of(uint4& v, int i) { return i == 0 ? 
 // One 16-byte vector per list, 32-bit word by word: the one (fp32) or two (16-bit types) elements of a
 // word are unpacked, run through the op and packed back before the next word is touched, so that few
 // values are live at a time; the packed Kahan tail then works on the word in place.
-template <typename T, class Op>
-__device__ __forceinline__ float compute_vec(Vecs<Op::NL>& v, const typename Op::Args& a, const typename Op::Ctx& ctx) {
+template <typename T, class Op, bool L2>
+__device__ __forceinline__ float compute_vec_as(Vecs<Op::NL>& v, const typename Op::Args& a, const typename Op::Ctx& ctx) {
   constexpr int EPW = Pack<T>::EPW;  // elements per word
   constexpr bool PACKED_TAIL = Op::kPackedTail && sizeof(T) == 2;
   float sum = 0.f;
@@ -407,7 +409,7 @@ __device__ __forceinline__ float compute_vec(Vecs<Op::NL>& v, const typename Op:
     }
 #pragma unroll
     for (int j = 0; j < EPW; j++) {
-      Op::template elem<T, !PACKED_TAIL>(e[j], a, ctx);
+      Op::template elem<T, !PACKED_TAIL, L2>(e[j], a, ctx);
       if (Op::kSumSlot >= 0) sum += e[j][Op::kSumSlot < 0 ? 0 : Op::kSumSlot];
     }
 #pragma unroll
@@ -435,13 +437,22 @@ __device__ __forceinline__ float compute_vec(Vecs<Op::NL>& v, const typename Op:
 }
 
 template <typename T, class Op>
+__device__ __forceinline__ float compute_vec(Vecs<Op::NL>& v, const typename Op::Args& a, const typename Op::Ctx& ctx) {
+  if constexpr (Op::kHasL2) {
+    if (Op::l2(a)) return compute_vec_as<T, Op, true>(v, a, ctx);
+  }
+  return compute_vec_as<T, Op, false>(v, a, ctx);
+}
+
+template <typename T, class Op>
 __device__ __forceinline__ float scalar_elem(T* const (&p)[Op::NL], int i, const typename Op::Args& a,
                                              const typename Op::Ctx& ctx) {
   float e[Op::NL];
 #pragma unroll
   for (int l = 0; l < Op::NL; l++) e[l] = Op::reads(l, a) ? Pack<T>::load1(p[l] + i) : 0.f;
   if constexpr (Op::kPull) e[1] = pull_one<T>(a.pull, p[1] + i);
-  Op::template elem<T, true>(e, a, ctx);
+  if (Op::kHasL2 && Op::l2(a)) Op::template elem<T, true, true>(e, a, ctx);
+  else Op::template elem<T, true, false>(e, a, ctx);
 #pragma unroll
   for (int l = 0; l < Op::NL; l++)
     if (Op::writes(l, a)) Pack<T>::store1(p[l] + i, e[l]);

@@ -641,7 +641,7 @@ int optimi_b200_adam(int n, void* const* params, void* const* grads, void* const
   a.l1 = make_lerp(beta1_comp);
   a.beta2_hat = (float)beta2_hat;
   a.beta2_comp = (float)beta2_comp;
-  a.wd = (float)weight_decay;
+  a.wd = weight_decay == 0 ? 1.0f : (float)weight_decay;  // the decay factor (or L2 coefficient); 1 = none
   a.eps = (float)eps;
   a.neg_lr = (float)(-lr);
   a.wd_mode = wd_mode_of(weight_decay, decouple_wd);
@@ -679,7 +679,7 @@ int optimi_b200_ranger(int n, void* const* params, void* const* grads, void* con
   a.l1 = make_lerp(beta1_comp);
   a.beta2_hat = (float)beta2_hat;
   a.beta2_comp = (float)beta2_comp;
-  a.wd = (float)weight_decay;
+  a.wd = weight_decay == 0 ? 1.0f : (float)weight_decay;  // the decay factor (or L2 coefficient); 1 = none
   a.eps = (float)eps;
   a.neg_lr = use_rect ? (float)(-lr * rect) : (float)(-lr);
   a.alpha = (float)alpha;
@@ -706,7 +706,7 @@ int optimi_b200_lion(int n, void* const* params, void* const* grads, void* const
   LionArgs a;
   a.l1 = make_lerp(beta1_comp);
   a.l2 = make_lerp(beta2_comp);
-  a.wd = (float)weight_decay;
+  a.wd = weight_decay == 0 ? 1.0f : (float)weight_decay;  // the decay factor (or L2 coefficient); 1 = none
   a.neg_lr = (float)(-lr);
   a.wd_mode = weight_decay != 0 ? kWdDecoupled : kWdNone;
   return dispatch<LionOp>("optimi_b200_lion", dtype, kahan, update, n, numels, lists, a, (cudaStream_t)stream);
@@ -727,7 +727,7 @@ int optimi_b200_sgd(int n, void* const* params, void* const* grads, void* const*
   SgdArgs a;
   a.damp = make_lerp(1 - momentum);
   a.momentum = (float)momentum;
-  a.wd = (float)weight_decay;
+  a.wd = weight_decay == 0 ? 1.0f : (float)weight_decay;  // the decay factor (or L2 coefficient); 1 = none
   a.neg_lr = (float)(-lr);
   a.wd_mode = wd_mode_of(weight_decay, decouple_wd);
   a.has_momentum = has_m;

@@ -10,10 +10,13 @@
 // Template flags: KAHAN = Kahan-compensated update (16-bit storage only), UPDATE = false is the
 // optimizer-accumulation micro-step (state averages only).
 //
-// Flag of elem<T, TAIL>: TAIL = false leaves the closing Kahan tail (p += k with the error fed back
+// Flags of elem<T, TAIL, L2>: TAIL = false leaves the closing Kahan tail (p += k with the error fed back
 // into k) to the caller, who does it on packed pairs (Pack<T>::kahan2) — an op offers this with
 // kPackedTail and names the slots with kSlotP / kSlotK; what must still happen to the parameter after
-// the tail goes into post_tail (kPostTail).
+// the tail goes into post_tail (kPostTail).  L2 = true is the launch with L2 weight decay (the gradient
+// gains wd*p); otherwise the parameter is multiplied by the launch's decay factor, which is 1 when
+// there is no decay (a product with 1 is exact).  Which of the two a launch is, is uniform, so the
+// caller branches once per vector (l2(args)) instead of the op testing a mode per element.
 #pragma once
 
 #include "mta_common.cuh"
@@ -58,10 +61,10 @@ __device__ __forceinline__ void adam_moments(float& m, float& v, float g, const 
   v = rnd<T>(__fmaf_rn(beta2_comp, __fmul_rn(g, g), v));
 }
 
-template <typename T>
-__device__ __forceinline__ void weight_decay(float& p, float& g, int mode, float wd) {
-  if (mode == kWdDecoupled) p = rnd<T>(__fmul_rn(p, wd));
-  else if (mode == kWdL2) g = rnd<T>(__fmaf_rn(wd, p, g));
+template <typename T, bool L2>
+__device__ __forceinline__ void weight_decay(float& p, float& g, float wd) {
+  if (L2) g = rnd<T>(__fmaf_rn(wd, p, g));
+  else p = rnd<T>(__fmul_rn(p, wd));
 }
 
 struct OpBase {
@@ -72,8 +75,10 @@ struct OpBase {
   static constexpr int kPull = 0;
   static constexpr bool kWholeTileBranch = false;
   static constexpr int kGradSlot = 1;  // the list that holds the gradients
-  static constexpr bool kPackedTail = false, kPostTail = false;
+  static constexpr bool kPackedTail = false, kPostTail = false, kHasL2 = false;
   static constexpr int kSlotP = 0, kSlotK = 0;
+  template <class Args>
+  static __device__ __forceinline__ bool l2(const Args&) { return false; }
   template <class Table, class Args>
   static __device__ __forceinline__ NoCtx context(const Table&, const Span&, const Args&) { return NoCtx{}; }
   template <typename T, class Args>
@@ -93,15 +98,16 @@ struct AdamArgs {
 template <bool KAHAN, bool UPDATE>
 struct AdamOp : OpBase {
   static constexpr int NL = 5, U = 1;
-  static constexpr bool kPackedTail = KAHAN && UPDATE;
+  static constexpr bool kPackedTail = KAHAN && UPDATE, kHasL2 = UPDATE;
   static constexpr int kSlotP = 0, kSlotK = 4;
   using Args = AdamArgs;
+  static __device__ __forceinline__ bool l2(const Args& a) { return a.wd_mode == kWdL2; }
   static __device__ __forceinline__ bool reads(int l, const Args&) { return l == 0 ? UPDATE : l == 4 ? KAHAN : true; }
   static __device__ __forceinline__ bool writes(int l, const Args&) { return l == 0 ? UPDATE : l == 4 ? KAHAN : l != 1; }
-  template <typename T, bool TAIL>
+  template <typename T, bool TAIL, bool L2>
   static __device__ __forceinline__ void elem(float (&e)[NL], const Args& a, const NoCtx&) {
     float &p = e[0], &g = e[1], &m = e[2], &v = e[3], &k = e[4];
-    if (UPDATE) weight_decay<T>(p, g, a.wd_mode, a.wd);
+    if (UPDATE) weight_decay<T, L2>(p, g, a.wd);
     adam_moments<T>(m, v, g, a.l1, a.beta2_hat, a.beta2_comp);
     if (UPDATE) {
       const float den = denominator<T>(v, a.eps);
@@ -139,17 +145,18 @@ struct PeerOp {
   static constexpr bool kPush = true;
   static constexpr int kPull = PULL;
   static constexpr bool kWholeTileBranch = false;
-  static constexpr bool kPackedTail = Base::kPackedTail, kPostTail = Base::kPostTail;
+  static constexpr bool kPackedTail = Base::kPackedTail, kPostTail = Base::kPostTail, kHasL2 = Base::kHasL2;
   static constexpr int kSlotP = Base::kSlotP, kSlotK = Base::kSlotK;
   using Args = PeerArgs<typename Base::Args>;
+  static __device__ __forceinline__ bool l2(const Args& a) { return Base::l2(a.base); }
   using Ctx = typename Base::Ctx;
   template <class Table>
   static __device__ __forceinline__ Ctx context(const Table& tab, const Span& s, const Args& a) { return Base::context(tab, s, a.base); }
   static __device__ __forceinline__ bool reads(int l, const Args& a) { return Base::reads(l, a.base); }
   static __device__ __forceinline__ bool writes(int l, const Args& a) { return Base::writes(l, a.base); }
-  template <typename T, bool TAIL>
+  template <typename T, bool TAIL, bool L2>
   static __device__ __forceinline__ void elem(float (&e)[NL], const Args& a, const Ctx& ctx) {
-    Base::template elem<T, TAIL>(e, a.base, ctx);
+    Base::template elem<T, TAIL, L2>(e, a.base, ctx);
   }
   template <typename T>
   static __device__ __forceinline__ float post_tail(float p, const Args& a) { return Base::template post_tail<T>(p, a.base); }
@@ -172,9 +179,10 @@ struct ScaledOp {
   static constexpr int kPull = 0;
   static constexpr bool kWholeTileBranch = Base::kWholeTileBranch;
   static constexpr int kGradSlot = Base::kGradSlot;
-  static constexpr bool kPackedTail = Base::kPackedTail, kPostTail = Base::kPostTail;
+  static constexpr bool kPackedTail = Base::kPackedTail, kPostTail = Base::kPostTail, kHasL2 = Base::kHasL2;
   static constexpr int kSlotP = Base::kSlotP, kSlotK = Base::kSlotK;
   using Args = ScaledArgs<typename Base::Args>;
+  static __device__ __forceinline__ bool l2(const Args& a) { return Base::l2(a.base); }
   struct Ctx {
     typename Base::Ctx base;
     float factor;
@@ -185,10 +193,10 @@ struct ScaledOp {
   }
   static __device__ __forceinline__ bool reads(int l, const Args& a) { return Base::reads(l, a.base); }
   static __device__ __forceinline__ bool writes(int l, const Args& a) { return Base::writes(l, a.base); }
-  template <typename T, bool TAIL>
+  template <typename T, bool TAIL, bool L2>
   static __device__ __forceinline__ void elem(float (&e)[NL], const Args& a, const Ctx& ctx) {
     e[kGradSlot] = rnd<T>(__fmul_rn(e[kGradSlot], ctx.factor));
-    Base::template elem<T, TAIL>(e, a.base, ctx.base);
+    Base::template elem<T, TAIL, L2>(e, a.base, ctx.base);
   }
   template <typename T>
   static __device__ __forceinline__ float post_tail(float p, const Args& a) { return Base::template post_tail<T>(p, a.base); }
@@ -210,7 +218,7 @@ struct SumSqOp : OpBase {
   using Args = SumSqArgs;
   static __device__ __forceinline__ bool reads(int l, const Args&) { return l == 0; }
   static __device__ __forceinline__ bool writes(int, const Args&) { return false; }
-  template <typename T, bool TAIL>
+  template <typename T, bool TAIL, bool L2>
   static __device__ __forceinline__ void elem(float (&e)[NL], const Args&, const NoCtx&) {
     e[1] = __fmul_rn(e[0], e[0]);
   }
@@ -235,17 +243,18 @@ struct RangerOp : OpBase {
   // six streams: <= 64 registers; five: as Adam (without the packed Kahan tail a little more is live)
   static constexpr int kMinBlocks = LOOK ? 8 : KAHAN ? OpBase::kMinBlocks : 10;
   // a lookahead step goes on after the tail (a second compensated sum into the slow weights): it keeps the fp32 form
-  static constexpr bool kPackedTail = KAHAN && UPDATE && !LOOK;
+  static constexpr bool kPackedTail = KAHAN && UPDATE && !LOOK, kHasL2 = UPDATE;
   static constexpr int kSlotP = 0, kSlotK = 4;
   using Args = RangerArgs;
+  static __device__ __forceinline__ bool l2(const Args& a) { return a.wd_mode == kWdL2; }
   static __device__ __forceinline__ bool reads(int l, const Args&) {
     return l == 0 ? UPDATE : l == 4 ? KAHAN : l == 5 ? (UPDATE && LOOK) : true;
   }
   static __device__ __forceinline__ bool writes(int l, const Args& a) { return l != 1 && reads(l, a); }
-  template <typename T, bool TAIL>
+  template <typename T, bool TAIL, bool L2>
   static __device__ __forceinline__ void elem(float (&e)[NL], const Args& a, const NoCtx&) {
     float &p = e[0], &g = e[1], &m = e[2], &v = e[3], &k = e[4], &la = e[5];
-    if (UPDATE) weight_decay<T>(p, g, a.wd_mode, a.wd);
+    if (UPDATE) weight_decay<T, L2>(p, g, a.wd);
     adam_moments<T>(m, v, g, a.l1, a.beta2_hat, a.beta2_comp);
     if (UPDATE) {
       float x = KAHAN ? k : p;
@@ -294,12 +303,12 @@ struct LionOp : OpBase {
   using Args = LionArgs;
   static __device__ __forceinline__ bool reads(int l, const Args&) { return l == 0 ? UPDATE : l == 3 ? KAHAN : true; }
   static __device__ __forceinline__ bool writes(int l, const Args& a) { return l != 1 && reads(l, a); }
-  template <typename T, bool TAIL>
+  template <typename T, bool TAIL, bool L2>
   static __device__ __forceinline__ void elem(float (&e)[NL], const Args& a, const NoCtx&) {
     float &p = e[0], &g = e[1], &m = e[2], &k = e[3];
     float u = 0.f;
     if (UPDATE) {
-      if (a.wd_mode == kWdDecoupled) p = rnd<T>(__fmul_rn(p, a.wd));
+      p = rnd<T>(__fmul_rn(p, a.wd));  // the decay factor, 1 without decay
       u = rnd<T>(lerp_op(m, g, a.l1));
       u = u > 0.f ? 1.f : (u < 0.f ? -1.f : 0.f);  // sign; NaN -> 0 like (0 < u) - (u < 0)
     }
@@ -328,17 +337,18 @@ struct SgdArgs {
 template <bool KAHAN, bool UPDATE>
 struct SgdOp : OpBase {
   static constexpr int NL = 4, U = 1;
-  static constexpr bool kPackedTail = KAHAN && UPDATE;
+  static constexpr bool kPackedTail = KAHAN && UPDATE, kHasL2 = UPDATE;
   static constexpr int kSlotP = 0, kSlotK = 3;
   using Args = SgdArgs;
+  static __device__ __forceinline__ bool l2(const Args& a) { return a.wd_mode == kWdL2; }
   static __device__ __forceinline__ bool reads(int l, const Args& a) {
     return l == 0 ? UPDATE : l == 2 ? a.has_momentum != 0 : l == 3 ? KAHAN : true;
   }
   static __device__ __forceinline__ bool writes(int l, const Args& a) { return l != 1 && reads(l, a); }
-  template <typename T, bool TAIL>
+  template <typename T, bool TAIL, bool L2>
   static __device__ __forceinline__ void elem(float (&e)[NL], const Args& a, const NoCtx&) {
     float &p = e[0], &g = e[1], &m = e[2], &k = e[3];
-    if (UPDATE) weight_decay<T>(p, g, a.wd_mode, a.wd);
+    if (UPDATE) weight_decay<T, L2>(p, g, a.wd);
     float upd = g;
     if (a.has_momentum) {
       if (a.dampening) {
@@ -385,7 +395,7 @@ struct AdanOp : OpBase {
   }
   static __device__ __forceinline__ bool reads(int l, const Args&) { return l == 0 ? UPDATE : l == 6 ? KAHAN : true; }
   static __device__ __forceinline__ bool writes(int l, const Args& a) { return l != 1 && reads(l, a); }
-  template <typename T, bool TAIL>
+  template <typename T, bool TAIL, bool L2>
   static __device__ __forceinline__ void elem(float (&e)[NL], const Args& a, const NoCtx&) {
     float &p = e[0], &g = e[1], &m = e[2], &d = e[3], &q = e[4], &pg = e[5], &k = e[6];
     float diff = rnd<T>(__fadd_rn(pg, g));
@@ -446,7 +456,7 @@ struct StableMomentsOp : OpBase {
   using Args = StableMomentsArgs;
   static __device__ __forceinline__ bool reads(int l, const Args&) { return l != 3; }
   static __device__ __forceinline__ bool writes(int l, const Args&) { return l == 1 || l == 2; }
-  template <typename T, bool TAIL>
+  template <typename T, bool TAIL, bool L2>
   static __device__ __forceinline__ void elem(float (&e)[NL], const Args& a, const NoCtx&) {
     float &g = e[0], &m = e[1], &v = e[2];
     adam_moments<T>(m, v, g, a.l1, a.beta2_hat, a.beta2_comp);
@@ -476,9 +486,10 @@ struct StableUpdateOp {
   static constexpr bool kPush = false;
   static constexpr int kPull = 0;
   static constexpr bool kWholeTileBranch = true;
-  static constexpr bool kPackedTail = KAHAN, kPostTail = false;
+  static constexpr bool kPackedTail = KAHAN, kPostTail = false, kHasL2 = false;
   static constexpr int kSlotP = 0, kSlotK = 3;
   using Args = StableUpdateArgs;
+  static __device__ __forceinline__ bool l2(const Args&) { return false; }
   using Ctx = float2;
   template <typename T>
   static __device__ __forceinline__ float post_tail(float p, const Args&) { return p; }
@@ -488,7 +499,7 @@ struct StableUpdateOp {
   }
   static __device__ __forceinline__ bool reads(int l, const Args&) { return l == 3 ? KAHAN : true; }
   static __device__ __forceinline__ bool writes(int l, const Args&) { return l == 0 || (l == 3 && KAHAN); }
-  template <typename T, bool TAIL>
+  template <typename T, bool TAIL, bool L2>
   static __device__ __forceinline__ void elem(float (&e)[NL], const Args& a, const float2& sc) {
     float &p = e[0], &m = e[1], &v = e[2], &k = e[3];
     if (a.has_wd) p = rnd<T>(__fmul_rn(p, sc.y));

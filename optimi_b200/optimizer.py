@@ -296,6 +296,25 @@ class OptimiOptimizer(Optimizer):
                     self._grad_factor = None
         return loss
 
+    @torch.no_grad()
+    def step_groups(self, indices: Iterable[int]) -> None:
+        """Steps only the parameter groups `param_groups[i]` for i in `indices` (each group keeps its own
+        step counter, so groups may be stepped at different moments): a caller whose gradients arrive in
+        pieces — copied in from the host, or reduced bucket by bucket — can step each piece as soon as it is
+        complete instead of waiting for the last one.  One call of `step()` equals `step_groups` over all
+        groups.  Not for a capturing stream."""
+        if torch.cuda.is_initialized() and torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("step_groups cannot be captured into a CUDA graph; capture step()")
+        factor = self._grad_factor
+        if factor is not None:
+            _lib.LIB.optimi_b200_grad_scale_begin(factor.data_ptr())
+        try:
+            for i in indices:
+                self._step_group(self.param_groups[i])
+        finally:
+            if factor is not None:
+                _lib.LIB.optimi_b200_grad_scale_end()
+
     # ---- gradient scaling fused into the step ----------------------------------------------------
     def set_grad_factor(self, factor: Tensor | None) -> None:
         """From now on every step multiplies each gradient element by `factor` (a CUDA float32 tensor with
