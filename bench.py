@@ -354,6 +354,72 @@ def measure_peer_copy_gbs(nbytes=1 << 30, repeats=5):
         return None
 
 
+def time_reference_gpu(device, steps=10):
+    """The reference's own CUDA back ends and this build on ONE list on this GPU (the 1.1 B Llama-style list, AdamW
+    bf16 + Kahan, decouple_lr): `optimi.AdamW(foreach=True)` and `(triton=True)` from the unmodified reference package
+    beside `optimi_b200.AdamW`, CUDA events around `steps` steps each after 3 warm-up steps."""
+    import warnings
+
+    import optimi_b200
+
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_dir, "optimi")):
+        return {"kind": "unavailable", "why": "reference package not present beside the repository"}
+    if ref_dir not in sys.path:
+        sys.path.insert(0, ref_dir)
+    import optimi
+
+    workload = "llama-1.1b"
+    shapes = WORKLOADS[workload]()
+    n = sum(numel(s) for s in shapes)
+    scales = grad_scales(len(shapes), seed=0)
+    out = {"workload": f"AdamW bf16+Kahan, {workload} parameter shapes ({n} params, {len(shapes)} tensors)", "steps": steps, "unit": "ms per step"}
+
+    def one(make, clobbers):
+        params = [p.requires_grad_(True) for p in make_params(shapes, device, torch.bfloat16, seed=0)]
+        gen = torch.Generator(device=device).manual_seed(5)
+        grads = []
+        for p, sc in zip(params, scales):
+            g = torch.empty_like(p)
+            fill_grad(g, sc, gen)
+            grads.append(g)
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore")
+            opt = make(params)
+
+        def step():
+            for p, g in zip(params, grads):
+                p.grad = g.clone() if clobbers else g  # the reference's foreach path uses its gradients as scratch
+            opt.step()
+
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize(device)
+        total = 0.0
+        for _ in range(steps):
+            for p, g in zip(params, grads):
+                p.grad = g.clone() if clobbers else g
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            opt.step()
+            e1.record()
+            e1.synchronize()
+            total += e0.elapsed_time(e1)
+        del opt, params, grads
+        torch.cuda.empty_cache()
+        return total / steps
+
+    out["optimi_b200"] = one(lambda ps: optimi_b200.AdamW(ps, **HYPER), False)
+    for key, kw, clobbers in (("reference_foreach", dict(foreach=True, triton=False), True), ("reference_triton", dict(foreach=False, triton=True), False)):
+        try:
+            out[key] = one(lambda ps: optimi.AdamW(ps, **HYPER, **kw), clobbers)
+        except Exception as exc:  # e.g. Triton cannot compile on this machine
+            out[key] = None
+            out[key + "_unavailable"] = f"{type(exc).__name__}: {exc}"[:200]
+    out["kind"] = "measured"
+    return out
+
+
 def run_b200_arm(args):
     import optimi_b200
     from optimi_b200 import _lib
@@ -591,6 +657,15 @@ def run_b200_arm(args):
                   "exchange_bound_ms": (pushed + pulled) / (link_gbs * 1e9) * 1e3,
                   "timed_over": "the fused step kernel" if sharded.exchange == "push" else "the all-gather"}
 
+    reference_gpu = None
+    if world == 1 and not args.no_reference_gpu:
+        del opt, host_grads, dev_grads, params, step_targets
+        import gc
+
+        gc.collect()
+        torch.cuda.empty_cache()
+        reference_gpu = time_reference_gpu(device)
+
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
         v, kind, cores, sample, _, _ = time_cpu_reference(args.workload, 12, 2, budget_s=20.0, optimizer=args.optimizer)
@@ -628,7 +703,7 @@ def run_b200_arm(args):
         "hbm_gbs": achieved, "step_ms": step_ms_max, "gather_ms": gather_ms_max, "wall_ms_per_step": t_wall * 1e3 / args.steps,
         "step_ms_spread_rank0": spread,
         "exchange_check": exchange_check, "local_step_ms": local_step_ms, "local_step_efficiency": local_eff, "bound": bound,
-        "roofline": roofline, "nvlink": nvlink, "cpu_baseline": cpu,
+        "roofline": roofline, "nvlink": nvlink, "cpu_baseline": cpu, "reference_gpu": reference_gpu,
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
                 "ms_per_step": e2e_s * 1e3, "steps": e2e_steps, "overlap": e2e_overlap},
         "gpu_launches": int(launches), "clocks": clocks.result, "library": os.path.relpath(_lib.LIB_PATH, ROOT),
@@ -755,6 +830,7 @@ def main():
     ap.add_argument("--workload", default="llama3-8b", choices=sorted(WORKLOADS) + ["gpt-gradient-release"])
     ap.add_argument("--optimizer", default="adamw", choices=sorted(OPTIMIZERS), help="default: the headline AdamW")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-reference-gpu", action="store_true", help="skip timing the reference's CUDA back ends on the 1.1 B list (N=1)")
     ap.add_argument("--reduce-grads", action="store_true", help="N>1 with the push exchange: also average the ranks' gradients inside the step kernel")
     ap.add_argument("--exchange", default="auto", choices=["auto", "push", "nccl"], help="N>1: how updated parameters reach the other ranks")
     args = ap.parse_args()
