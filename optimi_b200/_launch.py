@@ -25,11 +25,24 @@ def as_list(x: TensorList, n: int | None = None) -> list[Tensor | None] | None:
     return list(x)
 
 
+def is_dense(t: Tensor) -> bool:
+    """True when the tensor's elements fill one gap-free, non-overlapping block of memory in SOME order
+    of the dimensions (contiguous, channels_last, any transposition of a contiguous tensor)."""
+    if t.is_contiguous():
+        return True
+    expected = 1
+    for size, stride in sorted(((sz, st) for sz, st in zip(t.shape, t.stride()) if sz != 1), key=lambda x: x[1]):
+        if stride != expected:
+            return False
+        expected *= size
+    return True
+
+
 def _dense_like(t: Tensor, ref: Tensor) -> bool:
     if t.is_contiguous() and ref.is_contiguous():
         return True
     # any dense, non-overlapping layout works as long as every tensor of the element shares it
-    return t.stride() == ref.stride() and torch._prims_common.is_non_overlapping_and_dense(t)
+    return t.stride() == ref.stride() and is_dense(t)
 
 
 def _check_group(name: str, lists: list[list[Tensor] | None], list_names: Sequence[str]) -> None:

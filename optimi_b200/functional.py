@@ -31,6 +31,13 @@ def _advance(step: Tensor) -> int:
     return int(step.item())
 
 
+def _check_release(gradient_release: bool, foreach: bool, triton: bool) -> None:
+    """The one combination of back-end keywords the reference rejects (e.g. optimi/adam.py:278-282): the
+    per-parameter form of a step asked for together with the foreach back end and without Triton."""
+    if gradient_release and foreach and not triton:
+        raise ValueError(f"Gradient release {gradient_release=} and foreach {foreach=} cannot be used together")
+
+
 def adam(
     params: TensorList,
     grads: TensorList,
@@ -57,6 +64,7 @@ def adam(
 ):
     """Adam / AdamW step on lists of tensors (or bare tensors in gradient-release form)."""
     t = _advance(step)
+    _check_release(gradient_release, foreach, triton)
     tail = T.adam_tail(t, not optimizer_accumulation, lr=lr, beta1=beta1, beta2=beta2, weight_decay=weight_decay, eps=eps,
                        decouple_wd=decouple_wd, decouple_lr=decouple_lr, max_lr=max_lr, kahan_sum=kahan_sum)  # fmt: skip
     lists = [params, grads, exp_avgs, exp_avg_sqs, kahan_comps]
@@ -91,7 +99,7 @@ def adamw(
     adam(
         params, grads, exp_avgs, exp_avg_sqs, kahan_comps, lr=lr, beta1=beta1, beta2=beta2, weight_decay=weight_decay,
         eps=eps, step=step, decouple_wd=True, decouple_lr=decouple_lr, max_lr=max_lr, kahan_sum=kahan_sum,
-        gradient_release=gradient_release, optimizer_accumulation=optimizer_accumulation, _stream=_stream, _trusted=_trusted,
+        foreach=foreach, triton=triton, gradient_release=gradient_release, optimizer_accumulation=optimizer_accumulation, _stream=_stream, _trusted=_trusted,
     )  # fmt: skip
 
 
@@ -116,6 +124,7 @@ def lion(
     _trusted: bool = False,
 ):
     """Lion step.  Weight decay is always decoupled (optimi/lion.py:227-231)."""
+    _check_release(gradient_release, foreach, triton)
     tail = T.lion_tail(0, not optimizer_accumulation, lr=lr, beta1=beta1, beta2=beta2, weight_decay=weight_decay,
                        decouple_lr=decouple_lr, max_lr=max_lr, kahan_sum=kahan_sum)  # fmt: skip
     launch("optimi_b200_lion", [params, grads, exp_avgs, kahan_comps], ("params", "grads", "exp_avgs", "kahan_comps"),
@@ -144,6 +153,7 @@ def sgd(
     _trusted: bool = False,
 ):
     """SGD step with optional momentum, dampening and (decoupled) weight decay."""
+    _check_release(gradient_release, foreach, triton)
     if momentum == 0:
         exp_avgs = None
     tail = T.sgd_tail(0, not optimizer_accumulation, lr=lr, momentum=momentum, weight_decay=weight_decay, dampening=dampening,
@@ -153,15 +163,22 @@ def sgd(
 
 
 _workspaces: dict[tuple, Tensor] = {}
+_outgrown: list[Tensor] = []
 
 
 def _stable_workspace(device: torch.device, stream_id: int, nbytes: int) -> Tensor:
-    """Device scratch for StableAdamW's per-chunk partial sums, cached per (device, stream) and grown
-    on demand, so steady-state steps allocate nothing."""
+    """Device scratch for StableAdamW's per-chunk partial sums (and the gradient-norm passes), cached per
+    (device, stream) and grown on demand, so steady-state steps allocate nothing.  A buffer that has been
+    outgrown is kept for the life of the process instead of being handed back to the allocator: kernels
+    already enqueued on a side stream, or launches captured into a CUDA graph, may still name it, and the
+    allocator knows nothing about either (the buffers are used on raw stream handles).  They are small
+    (8 bytes per 512 elements of the largest list) and grow a handful of times at most."""
     key = (device, stream_id)
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
-        ws = torch.empty(max(nbytes, 1 << 16), dtype=torch.uint8, device=device)
+        if ws is not None:
+            _outgrown.append(ws)
+        ws = torch.empty(max(2 * nbytes, 1 << 16), dtype=torch.uint8, device=device)
         _workspaces[key] = ws
     return ws
 
@@ -202,6 +219,7 @@ def stableadamw(
     """StableAdamW step.  `eps_sqs` and `mean_squares` are accepted for signature compatibility; the
     kernels derive eps^2 from `eps` and keep the per-tensor mean square in their own scratch."""
     t = _advance(step)
+    _check_release(gradient_release, foreach, triton)
     update = not optimizer_accumulation
     scalars = T.stableadamw_tail(t, update, lr=lr, beta1=beta1, beta2=beta2, weight_decay=weight_decay, eps=eps,
                                  decouple_lr=decouple_lr, max_lr=max_lr, kahan_sum=kahan_sum)  # fmt: skip
@@ -247,6 +265,7 @@ def adan(
 ):
     """Adan step.  `prev_grads` holds the negated previous gradient."""
     t = _advance(step)
+    _check_release(gradient_release, foreach, triton)
     tail = T.adan_tail(t, not optimizer_accumulation, lr=lr, beta1=beta1, beta2=beta2, beta3=beta3, weight_decay=weight_decay,
                        eps=eps, decouple_lr=decouple_lr, max_lr=max_lr, adam_wd=adam_wd, kahan_sum=kahan_sum)  # fmt: skip
     launch(
@@ -281,6 +300,7 @@ def radam(
 ):
     """RAdam step: Adam averages with a rectified step once the variance estimate is trusted."""
     t = _advance(step)
+    _check_release(gradient_release, foreach, triton)
     tail = T.radam_tail(t, not optimizer_accumulation, lr=lr, beta1=beta1, beta2=beta2, weight_decay=weight_decay, eps=eps,
                         decouple_wd=decouple_wd, decouple_lr=decouple_lr, max_lr=max_lr, kahan_sum=kahan_sum)  # fmt: skip
     launch(
@@ -318,6 +338,7 @@ def ranger(
 ):
     """Ranger step: RAdam followed, on every k-th step, by a Lookahead pull toward the slow weights."""
     t = _advance(step)
+    _check_release(gradient_release, foreach, triton)
     tail = T.ranger_tail(t, not optimizer_accumulation, lr=lr, beta1=beta1, beta2=beta2, weight_decay=weight_decay, eps=eps,
                          k=k, alpha=alpha, decouple_wd=decouple_wd, decouple_lr=decouple_lr, max_lr=max_lr, kahan_sum=kahan_sum)  # fmt: skip
     launch(

@@ -23,7 +23,7 @@ import ctypes
 from . import _lib
 from . import _tails as T
 from . import functional as F
-from ._launch import _dense_like
+from ._launch import _dense_like, is_dense
 
 LOW_PRECISION = (torch.float16, torch.bfloat16)
 
@@ -31,6 +31,14 @@ LOW_PRECISION = (torch.float16, torch.bfloat16)
 def _check_range(name: str, value: float, shown: str | None = None):
     if not 0.0 <= value < 1.0:
         raise ValueError(f"Invalid {name} parameter: {shown or name}={value}")
+
+
+def _check_gradient(fn_name: str, grad: Tensor, param: Tensor) -> None:
+    """The kernels pair the elements of a gradient and its parameter by position in memory, so the two
+    must agree in dtype, device and memory layout (both contiguous, or the same dense strides: a
+    channels_last parameter needs a channels_last gradient)."""
+    if grad.dtype != param.dtype or grad.device != param.device or not _dense_like(grad, param):
+        raise RuntimeError(f"{fn_name}: a gradient does not match its parameter's dtype, device or layout")
 
 
 class _ReleasePlan:
@@ -102,9 +110,7 @@ class _SubPlan:
     def launch(self, tail: tuple, needs_workspace: bool) -> None:
         grads = [p.grad for p in self.params]
         for g, p in zip(grads, self.params):
-            if g.dtype != p.dtype or not g.is_contiguous():
-                if g.dtype != p.dtype or g.device != p.device or not _dense_like(g, p):
-                    raise RuntimeError(f"{self.fn_name}: a gradient does not match its parameter's dtype, device or layout")
+            _check_gradient(self.fn_name, g, p)
         self.grad_array[:] = list(map(Tensor.data_ptr, grads))
         stream_ptr = torch._C._cuda_getCurrentRawStream(self.index)
         if needs_workspace:
@@ -189,6 +195,7 @@ class OptimiOptimizer(Optimizer):
         self._group_plans: dict[int, _GroupPlan | None] = {}  # id(group) -> cached pointer tables of the whole-list step
         self.register_load_state_dict_post_hook(lambda opt: opt._drop_plans())
         self._release_stream: torch.cuda.Stream | None = None
+        self._release_stream_chosen = False  # use_release_stream was called: prepare_for_gradient_release keeps that choice
         self._release_fence_queued = False
         self._graph_nodes: _lib.GraphNodes | None = None  # kernel nodes of the step captured into a CUDA graph
         self._grad_factor: Tensor | None = None  # device scalar the next step(s) multiply the gradients by
@@ -248,7 +255,7 @@ class OptimiOptimizer(Optimizer):
     def _init_state(self, group: dict[str, Any], state: dict[str, Any], param: Tensor) -> None:
         if "kahan_comp" in state:
             return
-        if not param.is_contiguous() and not torch._prims_common.is_non_overlapping_and_dense(param):
+        if not param.is_contiguous() and not is_dense(param):
             raise RuntimeError("optimi_b200 needs dense parameters (contiguous or any permutation of contiguous)")
         self._new_state(group, state, param)
         state["kahan_comp"] = self._kahan_state(group, param)
@@ -352,7 +359,7 @@ class OptimiOptimizer(Optimizer):
         for g in grads:
             if g.device != g0.device:
                 raise NotImplementedError("clip_grad_norm: all gradients must live on one device")
-            if not g.is_contiguous() and not torch._prims_common.is_non_overlapping_and_dense(g):
+            if not g.is_contiguous() and not is_dense(g):
                 raise RuntimeError("clip_grad_norm: gradients must be dense")
         if self._clip_out is None or self._clip_out.device != g0.device:
             self._clip_out = torch.zeros(2, dtype=torch.float32, device=g0.device)
@@ -404,7 +411,7 @@ class OptimiOptimizer(Optimizer):
             g = t.grad
             if not g.is_cuda or g.dtype not in _lib.DTYPE_CODE or g.device != device:
                 raise RuntimeError("clip_grad_norm: gradients must be CUDA float32, bfloat16 or float16 tensors on one device")
-            if not g.is_contiguous() and not torch._prims_common.is_non_overlapping_and_dense(g):
+            if not g.is_contiguous() and not is_dense(g):
                 raise RuntimeError("clip_grad_norm: gradients must be dense")
             by_dtype.setdefault(g.dtype, []).append(i)
         with torch.cuda.device(device):
@@ -592,8 +599,9 @@ class OptimiOptimizer(Optimizer):
     # ---- gradient release on a side stream ----------------------------------------------------
     def use_release_stream(self, stream: torch.cuda.Stream | bool | None = True) -> None:
         """Runs the per-parameter steps of gradient release on a side stream so that they overlap
-        with the rest of the backward pass.  `True` creates a stream, `None`/`False` goes back to
-        stepping on the stream the hook fires on (the reference's behaviour).
+        with the rest of the backward pass (`prepare_for_gradient_release` switches this on by default for
+        CUDA models).  `True` creates a stream, `None`/`False` goes back to stepping on the stream the hook
+        fires on (the reference's behaviour).
 
         Ordering: each step waits for the gradient it consumes; the stream that runs the backward
         pass waits for all side-stream steps when the backward pass ends, so code after
@@ -602,6 +610,7 @@ class OptimiOptimizer(Optimizer):
         if stream is True:
             stream = torch.cuda.Stream()
         self._release_stream = stream or None
+        self._release_stream_chosen = True
 
     def _enter_release_stream(self, param: Tensor):
         side = self._release_stream

@@ -141,3 +141,100 @@ def test_full_size_against_reference_foreach(cname, hyper, steps, keys):
                 scale = torch.maximum(a.float().abs(), b.float().abs()).clamp_min(1e-3)
                 bad = (a.float() - b.float()).abs() > scale * 2.0**-7
                 assert not bool(bad.any()), f"{cname}: {name} of tensor {i}: {int(bad.sum())} elements more than 1 ulp apart"
+
+
+def _compare_with_reference(cname, hyper, steps, keys, shapes, scales, seed_base, label):
+    """Steps `shapes` (one chunk of a parameter list) `steps` times under both implementations with the same
+    seeded gradients and compares parameters and states; everything is freed on return."""
+    import optimi
+
+    import optimi_b200
+    from bench import make_params
+
+    mine = [p.requires_grad_(True) for p in make_params(shapes, "cuda", torch.bfloat16, seed=seed_base)]
+    theirs = [p.detach().clone().requires_grad_(True) for p in mine]
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        opt_ref = getattr(optimi, cname)(theirs, foreach=True, triton=False, **hyper)
+    opt_b200 = getattr(optimi_b200, cname)(mine, **hyper)
+    for step in range(steps):
+        gen = torch.Generator(device="cuda").manual_seed(1000 * seed_base + step)
+        for p, q, sc in zip(mine, theirs, scales):
+            g = torch.randn(p.shape, device="cuda", generator=gen).mul_(sc).to(torch.bfloat16)
+            p.grad = g
+            q.grad = g.clone()  # the reference's foreach path clobbers its gradients
+        opt_b200.step()
+        opt_ref.step()
+    torch.cuda.synchronize()
+    exact = cname != "StableAdamW"  # its per-tensor mean is summed in another order: 1 bf16 ulp
+    for i, (p, q) in enumerate(zip(mine, theirs)):
+        pairs = [("param", p.detach(), q.detach())] + [(k, opt_b200.state[p][k], opt_ref.state[q][k]) for k in keys]
+        for name, a, b in pairs:
+            if exact:
+                assert torch.equal(a, b), f"{cname}, {label}: {name} of tensor {i} {tuple(p.shape)} differs after {steps} steps"
+            else:
+                scale = torch.maximum(a.float().abs(), b.float().abs()).clamp_min(1e-3)
+                bad = (a.float() - b.float()).abs() > scale * 2.0**-7
+                assert not bool(bad.any()), f"{cname}, {label}: {name} of tensor {i}: {int(bad.sum())} elements more than 1 ulp apart"
+    n = sum(p.numel() for p in mine)
+    del mine, theirs, opt_ref, opt_b200
+    torch.cuda.empty_cache()
+    return n
+
+
+CONFIG3_RUNS = [
+    ("AdamW", dict(lr=3e-4, betas=(0.9, 0.99), weight_decay=1e-5, eps=1e-6, decouple_lr=True), ("exp_avg", "exp_avg_sq", "kahan_comp")),
+    ("Lion", dict(lr=1e-4, betas=(0.9, 0.99)), ("exp_avg", "kahan_comp")),
+    ("SGD", dict(lr=1e-2, momentum=0.9), ("exp_avg", "kahan_comp")),
+    ("StableAdamW", dict(lr=3e-4), ("exp_avg", "exp_avg_sq", "kahan_comp")),
+]
+
+
+@pytest.mark.parametrize("cname,hyper,keys", CONFIG3_RUNS, ids=[r[0] for r in CONFIG3_RUNS])
+def test_llama3_8b_list_against_reference_foreach_in_chunks(cname, hyper, keys):
+    """BASELINE config 3 at its stated size: all 8.03 B parameters of the Llama-3-8B list, bf16 + Kahan, against the
+    unmodified reference's foreach path on the same GPU.  Two full copies of the list with their states would not
+    fit beside each other, and the step is element-wise, so the list is walked in chunks (the embedding, four
+    decoder layers at a time, the head): each chunk is stepped 5 times under both implementations with the same
+    seeded gradients, compared bit for bit, and freed."""
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_dir, "optimi")):
+        pytest.skip("reference package not present beside the repository")
+    _need_free(60)
+    sys.path.insert(0, ref_dir)
+    sys.path.insert(0, ROOT)
+    from bench import WORKLOADS, grad_scales
+
+    shapes = WORKLOADS["llama3-8b"]()
+    scales = grad_scales(len(shapes), seed=0)
+    per_layer = 9
+    bounds = [0, 1] + [1 + per_layer * k for k in range(4, 32, 4)] + [1 + per_layer * 32, len(shapes)]
+    total = 0
+    for c, (a, b) in enumerate(zip(bounds[:-1], bounds[1:])):
+        total += _compare_with_reference(cname, hyper, 5, keys, shapes[a:b], scales[a:b], c + 1, f"tensors {a}..{b - 1} of the 8 B list")
+    assert total == 8030261248
+
+
+CONFIG4_RUNS = [
+    ("Adan", dict(lr=3e-4, betas=(0.98, 0.92, 0.99), kahan_sum=True), ("exp_avg", "exp_avg_diff", "exp_avg_sq", "prev_grad", "kahan_comp")),
+    ("Ranger", dict(lr=3e-4, k=6, alpha=0.5), ("exp_avg", "exp_avg_sq", "la_param", "kahan_comp")),
+]
+
+
+@pytest.mark.parametrize("cname,hyper,keys", CONFIG4_RUNS, ids=[r[0] for r in CONFIG4_RUNS])
+def test_llama_3b_list_adan_ranger_30_steps_against_reference(cname, hyper, keys):
+    """BASELINE config 4 at its stated size and step count: Adan (betas 0.98/0.92/0.99) and Ranger (k=6, alpha=0.5),
+    bf16 + Kahan, 30 steps on the whole 3 B Llama-style list at once (both copies with all their state tensors
+    resident), bit for bit against the unmodified reference's foreach path on the same GPU."""
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_dir, "optimi")):
+        pytest.skip("reference package not present beside the repository")
+    _need_free(130)
+    sys.path.insert(0, ref_dir)
+    sys.path.insert(0, ROOT)
+    from bench import WORKLOADS, grad_scales
+
+    shapes = WORKLOADS["llama-3b"]()
+    scales = grad_scales(len(shapes), seed=0)
+    n = _compare_with_reference(cname, hyper, 30, keys, shapes, scales, 7, "the 3 B list")
+    assert n == sum(int(torch.Size(s).numel()) for s in shapes)

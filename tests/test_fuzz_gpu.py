@@ -91,10 +91,12 @@ def test_random_configuration_matches_oracle(seed):
         for name, a, b in pairs:
             where = f"seed {seed} {opt} {dt} {kw} tensor {i} {tuple(p.shape)} {name}"
             if opt == "stableadamw":
+                # the per-tensor mean is summed in another order than the oracle's: 1e-6 relative (float32) over a floor of
+                # 1e-6 of the tensor's scale, 1 unit of the storage type (16-bit types) over a floor of 1e-3
                 if dt == "f32":
-                    ok = (a.double() - b.double()).abs() <= 1e-9 + 2e-6 * b.double().abs()
+                    ok = (a.double() - b.double()).abs() <= 1e-6 * b.double().abs() + 1e-6 * float(b.double().abs().max()) + 1e-30
                 else:
-                    ok = within_ulps_of_scale(a, b, 1.0, 1e-3) | ((a.double() - b.double()).abs() <= 1e-6)
+                    ok = within_ulps_of_scale(a, b, 1.0, 1e-3)
                 assert bool(ok.all()), f"{where}: {int((~ok).sum())} elements off"
             else:
                 same = torch.equal(a.view(torch.int32 if dt == "f32" else torch.int16), b.view(torch.int32 if dt == "f32" else torch.int16))

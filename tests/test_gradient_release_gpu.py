@@ -46,8 +46,7 @@ def test_hooks_match_oracle(oname, cname, kw, dtype, side_stream, accumulate):
     with warnings.catch_warnings():
         warnings.simplefilter("ignore")
         opt = getattr(optimi_b200, cname)(params, gradient_release=True, **kw)
-    if side_stream:
-        opt.use_release_stream(True)
+    opt.use_release_stream(bool(side_stream))  # explicit either way: prepare_for_gradient_release would default to a side stream
 
     recorded = []  # (iteration, param index, grad)
     index = {id(p): i for i, p in enumerate(params)}

@@ -227,3 +227,31 @@ def test_grad_factor_and_graph_entry_points_validate_on_the_host():
     released = optimi_b200.AdamW([p], lr=1e-3, gradient_release=True)
     with pytest.raises(RuntimeError, match="gradient_release"):
         released.clip_grad_norm(1.0)
+
+
+def test_gradient_layout_must_match_the_parameters():
+    """A contiguous gradient for a channels_last (dense but permuted) parameter would be applied to the wrong
+    elements: the per-step check refuses it, and accepts a gradient that shares the parameter's strides."""
+    from optimi_b200.optimizer import _check_gradient
+
+    p = torch.zeros(2, 3, 4, 5).to(memory_format=torch.channels_last)
+    assert not p.is_contiguous()
+    with pytest.raises(RuntimeError, match="does not match its parameter"):
+        _check_gradient("optimi_b200_adam", torch.zeros(2, 3, 4, 5), p)
+    _check_gradient("optimi_b200_adam", torch.zeros_like(p), p)  # zeros_like keeps the layout
+    with pytest.raises(RuntimeError, match="does not match its parameter"):
+        _check_gradient("optimi_b200_adam", torch.zeros(2, 3, 4, 5, dtype=torch.float64), torch.zeros(2, 3, 4, 5))
+    _check_gradient("optimi_b200_adam", torch.zeros(7), torch.zeros(7))
+
+
+def test_functional_refuses_gradient_release_with_foreach_like_the_reference():
+    import optimi_b200.functional as F
+
+    t = torch.zeros(4)
+    step = torch.tensor(0, dtype=torch.int32)
+    with pytest.raises(ValueError, match="cannot be used together"):
+        F.adam(t, t, t, t, lr=1e-3, beta1=0.9, beta2=0.99, weight_decay=0.0, eps=1e-6, step=step, decouple_wd=False,
+               foreach=True, gradient_release=True)
+    assert int(step) == 1  # the reference advances the counter before it chooses a back end (optimi/adam.py:261-282)
+    with pytest.raises(ValueError, match="cannot be used together"):
+        F.lion(t, t, t, lr=1e-3, beta1=0.9, beta2=0.99, weight_decay=0.0, foreach=True, gradient_release=True)
