@@ -442,7 +442,17 @@ def run_b200_arm(args):
         step_targets = params
         sharded = None
     else:
-        sharded = ShardedOptimizer(opt_cls, params, exchange=args.exchange, reduce_grads=args.reduce_grads, **opt_kw)
+        # the list goes in as 8 x N consecutive parameter groups (same options), so that the end-to-end path can step a
+        # rank's range in about eight pieces as its gradients land; the device-timed steps run all groups back to back
+        n_groups, target, acc, groups = 8 * world, n_params / (8 * world), 0, []
+        for p in params:
+            gi = min(n_groups - 1, int(acc / target))
+            while len(groups) <= gi:
+                groups.append({"params": []})
+            groups[gi]["params"].append(p)
+            acc += p.numel()
+        groups = [g for g in groups if g["params"]]
+        sharded = ShardedOptimizer(opt_cls, groups, exchange=args.exchange, reduce_grads=args.reduce_grads, **opt_kw)
         opt = sharded
         step_targets = sharded.shard_params
     n_local = sum(t.numel() for t in step_targets)
@@ -590,6 +600,34 @@ def run_b200_arm(args):
             for ci in range(len(chunks)):
                 main.wait_event(landed[ci])
                 opt.step_groups([ci])
+            result_host.copy_(result_src.detach(), non_blocking=True)
+            main.synchronize()
+
+    elif not args.reduce_grads:
+        # N > 1: the same, over this rank's pieces of each parameter group (ShardedOptimizer.begin_step / step_groups /
+        # end_step); a rank's range touches about eight of the 8 x N groups
+        index_of = {id(t): i for i, t in enumerate(step_targets)}
+        pieces_of_group = [[index_of[id(sp)] for sp in g["params"]] for g in sharded.inner.param_groups]
+        mine = [gi for gi, idx in enumerate(pieces_of_group) if idx]
+        copy_stream = torch.cuda.Stream(device)
+        landed = {gi: torch.cuda.Event() for gi in mine}
+        e2e_overlap = {"chunks": len(mine), "how": "this rank's gradient pieces copied group by group on a side stream, each group stepped "
+                       "(and pushed) when its copy has landed"}  # fmt: skip
+
+        def step_e2e():
+            main = torch.cuda.current_stream(device)
+            copy_stream.wait_stream(main)
+            with torch.cuda.stream(copy_stream):
+                for gi in mine:
+                    for i in pieces_of_group[gi]:
+                        dev_grads[i].copy_(host_grads[i], non_blocking=True)
+                    landed[gi].record(copy_stream)
+            sharded.begin_step(dev_grads)
+            for gi in range(len(pieces_of_group)):
+                if gi in landed:
+                    main.wait_event(landed[gi])
+                sharded.step_groups([gi])  # every group on every rank: the step counters of all groups advance together
+            sharded.end_step()
             result_host.copy_(result_src.detach(), non_blocking=True)
             main.synchronize()
 

@@ -150,9 +150,14 @@ int optimi_b200_adam(int n_tensors, void* const* params, void* const* grads, voi
  * of 16.  Between optimi_b200_push_begin and optimi_b200_push_end every parameter-updating launch
  * the CALLING THREAD makes through any entry point of this library stores each updated parameter
  * vector locally and, with plain peer stores over NVLink, at the same offset in every peer's copy,
- * tile by tile as the step proceeds.  The kernels wait for nobody; the caller must order the ranks
- * after the launches (any stream-ordered collective or barrier) before the pushed values are read
- * on the peers.  Accumulation-only steps (update_parameters == 0) push nothing. */
+ * tile by tile as the step proceeds.  The kernels wait for nobody, so the caller orders the ranks on
+ * BOTH sides of the launches (any stream-ordered collective or barrier will do): before them, so that
+ * no peer is still reading the parameter buffer this rank is about to store into (its forward,
+ * backward or evaluation pass must have finished on every rank), and after them, before the pushed
+ * values are read on the peers.  Blocks start their round over the peers at different peers, so the
+ * order of the entries of `peer_deltas` does not matter.  Accumulation-only steps
+ * (update_parameters == 0) push nothing.  Composes with optimi_b200_grad_scale_begin (the gradients
+ * are scaled on load, the parameters pushed on store). */
 int optimi_b200_push_begin(int n_peers, const int64_t* peer_deltas);
 void optimi_b200_push_end(void);
 

@@ -57,34 +57,48 @@ N_PARTS = 3  # the source compiles as independent translation units (OPTIMI_PART
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
+    """Compiles the library unless it is current.  Safe against several processes arriving at once (the ranks of
+    a multi-GPU job importing the package with a stale library): one builds under a file lock, into a private
+    directory, and moves the result into place in one step; the others wait and find it current."""
     if not force and up_to_date():
         return LIB
+    import fcntl
+    import tempfile
+
     os.makedirs(LIB_DIR, exist_ok=True)
-    nvcc = find_nvcc()
-    ccbin = ["-ccbin", "/usr/bin/g++"] if os.path.exists("/usr/bin/g++") else []  # the image's CC/CXX point at a wrapper
-    compile_flags = [f for f in NVCC_FLAGS if f not in ("-shared", "--use-local-env")]
-    objs, procs = [], []
-    for part in range(N_PARTS):
-        obj = os.path.join(LIB_DIR, f"part{part}.o")
-        objs.append(obj)
-        cmd = [nvcc, *ccbin, *compile_flags, *(["-Xptxas", "-v"] if verbose else []), f"-DOPTIMI_PART={part}", "-c", "-o", obj, SRC]
-        procs.append((cmd, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)))
-    log = ""
-    for cmd, p in procs:
-        out, err = p.communicate()
-        log += out + err
-        if p.returncode != 0:
-            raise RuntimeError("nvcc failed:\n" + " ".join(cmd) + "\n" + out + err)
-    link = [nvcc, *ccbin, "-shared", "-o", LIB, *objs]
-    res = subprocess.run(link, capture_output=True, text=True)
-    if res.returncode != 0:
-        raise RuntimeError("link failed:\n" + " ".join(link) + "\n" + res.stdout + res.stderr)
-    for obj in objs:
-        os.remove(obj)
-    if verbose:
-        print(log)
-    with open(STAMP, "w") as fh:
-        fh.write(source_hash())
+    with open(os.path.join(LIB_DIR, ".build.lock"), "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        if not force and up_to_date():  # another process built it while this one waited
+            return LIB
+        nvcc = find_nvcc()
+        ccbin = ["-ccbin", "/usr/bin/g++"] if os.path.exists("/usr/bin/g++") else []  # the image's CC/CXX point at a wrapper
+        compile_flags = [f for f in NVCC_FLAGS if f not in ("-shared", "--use-local-env")]
+        with tempfile.TemporaryDirectory(dir=LIB_DIR, prefix=".build-") as tmp:
+            objs, procs = [], []
+            for part in range(N_PARTS):
+                obj = os.path.join(tmp, f"part{part}.o")
+                objs.append(obj)
+                cmd = [nvcc, *ccbin, *compile_flags, *(["-Xptxas", "-v"] if verbose else []), f"-DOPTIMI_PART={part}", "-c", "-o", obj, SRC]
+                procs.append((cmd, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)))
+            log = ""
+            for cmd, p in procs:
+                out, err = p.communicate()
+                log += out + err
+                if p.returncode != 0:
+                    raise RuntimeError("nvcc failed:\n" + " ".join(cmd) + "\n" + out + err)
+            fresh = os.path.join(tmp, "liboptimi_b200.so")
+            link = [nvcc, *ccbin, "-shared", "-o", fresh, *objs]
+            res = subprocess.run(link, capture_output=True, text=True)
+            if res.returncode != 0:
+                raise RuntimeError("link failed:\n" + " ".join(link) + "\n" + res.stdout + res.stderr)
+            if os.path.exists(STAMP):
+                os.remove(STAMP)  # never a current stamp beside an older library
+            os.replace(fresh, LIB)
+        if verbose:
+            print(log)
+        with open(STAMP + ".tmp", "w") as fh:
+            fh.write(source_hash())
+        os.replace(STAMP + ".tmp", STAMP)
     return LIB
 
 

@@ -430,6 +430,41 @@ class ShardedOptimizer:
         self.step_local(shard_grads)
         self.gather_params()
 
+    # a step in pieces: begin_step(); step_groups([...]) as often as needed, each group once; end_step() -----
+    @torch.no_grad()
+    def begin_step(self, shard_grads: list[Tensor] | None = None) -> None:
+        """Opens a step whose parameter groups are stepped one after another with `step_groups`, for gradients
+        that arrive in pieces (copied in from the host, or reduced bucket by bucket): binds the gradients and,
+        under the push exchange, holds the meeting that must precede the first pushing launch."""
+        if self.reduce_grads:
+            raise NotImplementedError("a step in pieces is not available with reduce_grads=True")
+        if shard_grads is None:
+            self._bind_grads()
+        else:
+            for sp, g in zip(self.shard_params, shard_grads):
+                sp.grad = g
+        if self.exchange == "push" and self.pre_step_sync:
+            dist.all_reduce(self._meet, group=self.group)
+
+    @torch.no_grad()
+    def step_groups(self, indices) -> None:
+        """Steps this rank's pieces of the parameter groups `indices` (pushing them to the peers under the push
+        exchange).  Between `begin_step()` and `end_step()`; every group exactly once per step."""
+        if not hasattr(self.inner, "step_groups"):
+            raise NotImplementedError("step_groups needs an optimi_b200 optimizer")
+        if self.exchange == "push":
+            from ._lib import peer_push
+
+            with peer_push(self._peer_deltas):
+                self.inner.step_groups(indices)
+        else:
+            self.inner.step_groups(indices)
+
+    @torch.no_grad()
+    def end_step(self) -> None:
+        """Closes a step in pieces: the exchange (all-gather, or the meeting that follows the pushes)."""
+        self.gather_params()
+
     def zero_grad(self, set_to_none: bool = True):
         if self.reduce_grads:  # gradients stay attached to the shared buffer; call after step() (its closing collective
             for b in self.buckets:  # guarantees no rank is still reading)

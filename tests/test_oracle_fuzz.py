@@ -79,8 +79,13 @@ def test_oracle_matches_reference_on_random_configurations_from_a_gpu(seed):
             got, want = got.reshape(-1), want.reshape(-1)
             where = f"seed {seed} {opt} {kw} tensor {i} {name}"
             if opt == "stableadamw":
+                # float16 with a tiny eps: eps^2 underflows to zero, an untouched element then divides 0 by 0, and whole
+                # tensors go NaN or infinite in the reference as in the oracle; those must sit at the same places
+                same_special = (got.isnan() & want.isnan()) | (got.isinf() & want.isinf() & (got.sign() == want.sign()))
+                finite = got.isfinite() & want.isfinite()
+                assert bool((same_special | finite).all()), f"{where}: NaN / infinity at different places"
                 ok = (got.double() - want.double()).abs() <= 1e-6 + (2e-6 if got.dtype == torch.float32 else 2**-7) * want.double().abs()
-                assert bool(ok.all()), f"{where}: {int((~ok).sum())} elements off"
+                assert bool((ok | same_special).all()), f"{where}: {int((~(ok | same_special)).sum())} elements off"
             else:
                 d = ulp_diff(got, want)
                 d[got.isnan() & want.isnan()] = 0

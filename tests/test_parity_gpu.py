@@ -244,3 +244,29 @@ def test_config1_full_size():
             key = f"config1/{i}.{name}"
             if key in CUDA.files:
                 assert torch.equal(got.cpu().reshape(-1)[::CONFIG1_STRIDE], torch.from_numpy(CUDA[key].copy())), f"tensor {i} {name} differs from the reference"
+
+
+def test_permuted_dense_parameter_steps_like_its_memory():
+    """The kernels pair elements by position in memory, so a dense but permuted parameter (a transposed view, a
+    channels_last weight) whose gradient and states share its strides must end up exactly like the same memory
+    stepped as a contiguous tensor; a gradient with other strides is refused."""
+    import optimi_b200
+
+    gen = torch.Generator().manual_seed(0)
+    base = (torch.randn(64, 48, generator=gen) * 0.02).to(torch.bfloat16).cuda()
+    grads = [(torch.randn(64, 48, generator=gen) * 1e-3).to(torch.bfloat16).cuda() for _ in range(3)]
+    p = torch.nn.Parameter(base.clone().t())  # 48 x 64 with strides (1, 48): dense, not contiguous
+    q = torch.nn.Parameter(base.clone())
+    assert not p.is_contiguous()
+    kw = dict(lr=1e-3, weight_decay=1e-2)
+    a, b = optimi_b200.AdamW([p], **kw), optimi_b200.AdamW([q], **kw)
+    for g in grads:
+        p.grad, q.grad = g.t(), g
+        a.step()
+        b.step()
+    torch.cuda.synchronize()
+    assert torch.equal(p.detach().t(), q.detach())
+    assert torch.equal(a.state[p]["exp_avg_sq"].t(), b.state[q]["exp_avg_sq"])
+    p.grad = grads[0].t().contiguous()  # same shape, other strides
+    with pytest.raises(RuntimeError, match="does not match its parameter"):
+        a.step()

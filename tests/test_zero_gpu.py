@@ -172,6 +172,37 @@ def case_replica_check_sees_a_flipped_bit(rank, world):
     return "a flipped bit on one rank went unnoticed" if seen else ""
 
 
+def case_step_in_pieces(rank, world, exchange):
+    """begin_step / step_groups / end_step over three parameter groups equals one step() of an unsharded optimizer."""
+    import optimi_b200
+    from optimi_b200.zero import ShardedOptimizer
+
+    dev = torch.device("cuda", rank)
+    g = torch.Generator().manual_seed(0)
+    host = _host_params(g)
+    params = [torch.nn.Parameter(h.clone().to(dev)) for h in host]
+    ref = [torch.nn.Parameter(h.clone().to(dev)) for h in host]
+
+    def groups(ps):
+        return [{"params": ps[0:2]}, {"params": ps[2:3], "weight_decay": 0.0}, {"params": ps[3:]}]
+
+    kw = dict(lr=3e-4, weight_decay=1e-2)
+    sharded = ShardedOptimizer(optimi_b200.AdamW, groups(params), exchange=exchange, **kw)
+    plain = optimi_b200.AdamW(groups(ref), **kw)
+    for _ in range(4):
+        grads = [(torch.randn(s, generator=g) * 1e-3).to(torch.bfloat16).to(dev) for s in SHAPES]
+        for p, r, gr in zip(params, ref, grads):
+            p.grad, r.grad = gr.clone(), gr.clone()
+        sharded.begin_step()
+        for gi in (2, 0, 1):  # any order, each group once
+            sharded.step_groups([gi])
+        sharded.end_step()
+        plain.step()
+        sharded.zero_grad()
+    torch.cuda.synchronize()
+    return "" if _same(params, ref) else "a step in pieces differs from the unsharded step"
+
+
 def _reference_package():
     ref_dir = os.path.join(ROOT, "baseline", "_ref")
     if not os.path.isdir(os.path.join(ref_dir, "optimi")):
@@ -277,6 +308,8 @@ CASES = {
     "groups-dtypes-clip-nccl": (case_param_groups_mixed_dtypes_and_clip, ("nccl", True)),
     "groups-dtypes-clip-push": (case_param_groups_mixed_dtypes_and_clip, ("push", True)),
     "replica-check": (case_replica_check_sees_a_flipped_bit, ()),
+    "step-in-pieces-nccl": (case_step_in_pieces, ("nccl",)),
+    "step-in-pieces-push": (case_step_in_pieces, ("push",)),
     "checkpoint-reference-Adan": (case_checkpoint_round_trip_with_reference, ("Adan", dict(lr=3e-4, kahan_sum=True), True)),
     "checkpoint-reference-StableAdamW": (case_checkpoint_round_trip_with_reference, ("StableAdamW", dict(lr=3e-4), False)),
 }
