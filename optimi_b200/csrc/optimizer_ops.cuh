@@ -61,10 +61,17 @@ __device__ __forceinline__ void adam_moments(float& m, float& v, float g, const 
   v = rnd<T>(__fmaf_rn(beta2_comp, __fmul_rn(g, g), v));
 }
 
-template <typename T, bool L2>
+// A value that goes nowhere but into its list's store needs no rounding of its own: packing it for the store
+// (Pack<T>::pack_word, store1) IS that rounding.  ROUND = false marks such a last op; the packed Kahan tail
+// counts as a store here, because it starts from the packed words.
+template <typename T, bool ROUND>
+__device__ __forceinline__ float rnd_if(float x) { return ROUND ? rnd<T>(x) : x; }
+
+// ROUND_P: the decayed parameter is used again by this element's arithmetic (false: it only goes to the tail / store)
+template <typename T, bool L2, bool ROUND_P>
 __device__ __forceinline__ void weight_decay(float& p, float& g, float wd) {
   if (L2) g = rnd<T>(__fmaf_rn(wd, p, g));
-  else p = rnd<T>(__fmul_rn(p, wd));
+  else p = rnd_if<T, ROUND_P>(__fmul_rn(p, wd));
 }
 
 struct OpBase {
@@ -107,15 +114,15 @@ struct AdamOp : OpBase {
   template <typename T, bool TAIL, bool L2>
   static __device__ __forceinline__ void elem(float (&e)[NL], const Args& a, const NoCtx&) {
     float &p = e[0], &g = e[1], &m = e[2], &v = e[3], &k = e[4];
-    if (UPDATE) weight_decay<T, L2>(p, g, a.wd);
+    if (UPDATE) weight_decay<T, L2, !KAHAN || TAIL>(p, g, a.wd);
     adam_moments<T>(m, v, g, a.l1, a.beta2_hat, a.beta2_comp);
     if (UPDATE) {
       const float den = denominator<T>(v, a.eps);
       if (KAHAN) {
-        k = rnd<T>(addcdiv_op<T>(k, m, den, a.neg_lr));
+        k = rnd_if<T, TAIL>(addcdiv_op<T>(k, m, den, a.neg_lr));
         if (TAIL) kahan_tail<T>(p, k);
       } else {
-        p = rnd<T>(addcdiv_op<T>(p, m, den, a.neg_lr));
+        p = addcdiv_op<T>(p, m, den, a.neg_lr);  // rounded by the store
       }
     }
   }
@@ -254,12 +261,13 @@ struct RangerOp : OpBase {
   template <typename T, bool TAIL, bool L2>
   static __device__ __forceinline__ void elem(float (&e)[NL], const Args& a, const NoCtx&) {
     float &p = e[0], &g = e[1], &m = e[2], &v = e[3], &k = e[4], &la = e[5];
-    if (UPDATE) weight_decay<T, L2>(p, g, a.wd);
+    constexpr bool kMore = LOOK || (KAHAN && TAIL);  // the step's result is used again before it is stored
+    if (UPDATE) weight_decay<T, L2, !KAHAN || kMore>(p, g, a.wd);
     adam_moments<T>(m, v, g, a.l1, a.beta2_hat, a.beta2_comp);
     if (UPDATE) {
       float x = KAHAN ? k : p;
-      if (a.use_rect) x = rnd<T>(addcdiv_op<T>(x, m, denominator<T>(v, a.eps), a.neg_lr));
-      else x = rnd<T>(__fmaf_rn(a.neg_lr, m, x));
+      if (a.use_rect) x = rnd_if<T, kMore>(addcdiv_op<T>(x, m, denominator<T>(v, a.eps), a.neg_lr));
+      else x = rnd_if<T, kMore>(__fmaf_rn(a.neg_lr, m, x));
       if (KAHAN) {
         k = x;
         if (TAIL || LOOK) kahan_tail<T>(p, k);
@@ -308,17 +316,17 @@ struct LionOp : OpBase {
     float &p = e[0], &g = e[1], &m = e[2], &k = e[3];
     float u = 0.f;
     if (UPDATE) {
-      p = rnd<T>(__fmul_rn(p, a.wd));  // the decay factor, 1 without decay
+      p = rnd_if<T, !KAHAN || TAIL>(__fmul_rn(p, a.wd));  // the decay factor, 1 without decay
       u = rnd<T>(lerp_op(m, g, a.l1));
       u = u > 0.f ? 1.f : (u < 0.f ? -1.f : 0.f);  // sign; NaN -> 0 like (0 < u) - (u < 0)
     }
-    m = rnd<T>(lerp_op(m, g, a.l2));
+    m = lerp_op(m, g, a.l2);  // rounded by the store
     if (UPDATE) {
       if (KAHAN) {
-        k = rnd<T>(__fmaf_rn(a.neg_lr, u, k));
+        k = rnd_if<T, TAIL>(__fmaf_rn(a.neg_lr, u, k));
         if (TAIL) kahan_tail<T>(p, k);
       } else {
-        p = rnd<T>(__fmaf_rn(a.neg_lr, u, p));
+        p = __fmaf_rn(a.neg_lr, u, p);  // rounded by the store
       }
     }
   }
@@ -395,7 +403,7 @@ struct AdanOp : OpBase {
   // Adan-style weight decay divides the parameter after the step (optimi/adan.py:546)
   template <typename T>
   static __device__ __forceinline__ float post_tail(float p, const Args& a) {
-    return a.wd_mode == 2 ? rnd<T>(__fmul_rn(p, a.wd_mul)) : p;
+    return a.wd_mode == 2 ? __fmul_rn(p, a.wd_mul) : p;  // rounded when it is packed for the store
   }
   static __device__ __forceinline__ bool reads(int l, const Args&) { return l == 0 ? UPDATE : l == 6 ? KAHAN : true; }
   static __device__ __forceinline__ bool writes(int l, const Args& a) { return l != 1 && reads(l, a); }
@@ -412,7 +420,7 @@ struct AdanOp : OpBase {
     pg = -g;
     if (UPDATE) {
       const float den = denominator<T>(q, a.eps);
-      if (a.wd_mode == 1) p = rnd<T>(__fmul_rn(p, a.wd_mul));
+      if (a.wd_mode == 1) p = rnd_if<T, !KAHAN || TAIL>(__fmul_rn(p, a.wd_mul));
       // both quotients share the denominator, and with it the reciprocal of the shortcut
       float qm, qd;
       if constexpr (sizeof(T) == 2) {
@@ -425,7 +433,7 @@ struct AdanOp : OpBase {
       }
       if (KAHAN) {
         k = rnd<T>(__fmaf_rn(a.neg_lr, qm, k));
-        k = rnd<T>(__fmaf_rn(a.neg_lr_beta2, qd, k));
+        k = rnd_if<T, TAIL>(__fmaf_rn(a.neg_lr_beta2, qd, k));
         if (TAIL) {
           kahan_tail<T>(p, k);
           p = post_tail<T>(p, a);
@@ -433,7 +441,7 @@ struct AdanOp : OpBase {
       } else {
         p = rnd<T>(__fmaf_rn(a.neg_lr, qm, p));
         p = rnd<T>(__fmaf_rn(a.neg_lr_beta2, qd, p));
-        if (a.wd_mode == 2) p = rnd<T>(__fmul_rn(p, a.wd_mul));
+        if (a.wd_mode == 2) p = __fmul_rn(p, a.wd_mul);  // rounded by the store
       }
     }
   }
@@ -506,13 +514,13 @@ struct StableUpdateOp {
   template <typename T, bool TAIL, bool L2>
   static __device__ __forceinline__ void elem(float (&e)[NL], const Args& a, const float2& sc) {
     float &p = e[0], &m = e[1], &v = e[2], &k = e[3];
-    if (a.has_wd) p = rnd<T>(__fmul_rn(p, sc.y));
+    if (a.has_wd) p = rnd_if<T, !KAHAN || TAIL>(__fmul_rn(p, sc.y));
     const float den = denominator<T>(v, a.eps);
     if (KAHAN) {
-      k = rnd<T>(addcdiv_op<T>(k, m, den, sc.x));
+      k = rnd_if<T, TAIL>(addcdiv_op<T>(k, m, den, sc.x));
       if (TAIL) kahan_tail<T>(p, k);
     } else {
-      p = rnd<T>(addcdiv_op<T>(p, m, den, sc.x));
+      p = addcdiv_op<T>(p, m, den, sc.x);  // rounded by the store
     }
   }
 };

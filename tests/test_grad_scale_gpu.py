@@ -194,3 +194,40 @@ def test_gradient_release_applies_the_factor():
             assert torch.equal(manual.state[p][k], hooked.state[q][k]), k
     with pytest.raises(RuntimeError, match="gradient_release"):
         hooked.clip_grad_norm(1.0)
+
+
+@pytest.mark.parametrize("max_norm", [0.05, 1e4])
+def test_clip_factor_over_mixed_dtypes_matches_torch(max_norm):
+    """float32 embeddings beside a bfloat16 body (what `to_low_precision` leaves): per-tensor norms in each tensor's
+    dtype, the total norm and the coefficient in float32, as torch.nn.utils.clip_grad_norm_ promotes them; then a step
+    with the coefficient equals scaling the gradients (each in its own dtype) and stepping plainly."""
+    import optimi_b200
+
+    gen = torch.Generator().manual_seed(9)
+    dtypes = [torch.float32, torch.bfloat16, torch.bfloat16, torch.float32, torch.bfloat16]
+    shapes = [(300, 64), (257, 129), (4096,), (7,), (1000, 33)]
+    host = [(torch.randn(s, generator=gen) * 0.02).to(d) for s, d in zip(shapes, dtypes)]
+    fused = [torch.nn.Parameter(h.clone().cuda()) for h in host]
+    plain = [torch.nn.Parameter(h.clone().cuda()) for h in host]
+    shadow = [torch.nn.Parameter(h.clone().cuda()) for h in host]
+    for p, q, s in zip(fused, plain, shadow):
+        g = (torch.randn(p.shape, generator=gen) * 1e-2).to(p.dtype).cuda()
+        p.grad, s.grad = g.clone(), g.clone()
+    opt = optimi_b200.AdamW(fused, lr=1e-3)
+    total = opt.clip_grad_norm(max_norm)
+    factor = opt._grad_factor.clone()
+    ref_total = torch.nn.utils.clip_grad_norm_(shadow, max_norm, foreach=True)
+    ref_factor = torch.clamp(max_norm / (ref_total + 1e-6), max=1.0)
+    assert ref_total.dtype == torch.float32
+    assert abs(float(total) - float(ref_total)) <= 2 * _ulp(ref_total, torch.float32) + 1e-6 * float(ref_total)
+    assert abs(float(factor) - float(ref_factor)) <= 1e-6 * float(ref_factor) + 1e-12
+    assert (float(factor) == 1.0) == (max_norm == 1e4)
+    # stepping with the coefficient == scaling each gradient in its own dtype, then stepping
+    ref_opt = optimi_b200.AdamW(plain, lr=1e-3)
+    for p, q in zip(fused, plain):
+        q.grad = (p.grad.float() * factor).to(p.dtype)
+    opt.step()
+    ref_opt.step()
+    torch.cuda.synchronize()
+    for p, q in zip(fused, plain):
+        assert torch.equal(p.detach(), q.detach()), f"{p.dtype} tensor {tuple(p.shape)} differs"

@@ -264,3 +264,20 @@ def test_param_groups_and_mixed_dtypes_match_unsharded():
     assert values, "consolidated state differs from the unsharded optimizer's"
     assert cont, "the run continued from the consolidated checkpoint diverges"
     assert identical, "check_replicas() reports differing ranks"
+
+
+def test_layout_digest_covers_what_decides_the_layout():
+    from optimi_b200.zero import _as_groups, layout_digest
+
+    a = [torch.zeros(10), torch.zeros(3, 4), torch.zeros(5, dtype=torch.float64)]
+    base = layout_digest(_as_groups(a), 2, "AdamW", False, "push")
+    assert base == layout_digest(_as_groups([torch.ones(10), torch.ones(3, 4), torch.ones(5, dtype=torch.float64)]), 2, "AdamW", False, "push")
+    different = [
+        layout_digest(_as_groups([torch.zeros(11), a[1], a[2]]), 2, "AdamW", False, "push"),  # a size
+        layout_digest(_as_groups([a[0], a[1], torch.zeros(5)]), 2, "AdamW", False, "push"),  # a dtype
+        layout_digest(_as_groups([{"params": a[:1]}, {"params": a[1:]}]), 2, "AdamW", False, "push"),  # the grouping
+        layout_digest(_as_groups(a), 4, "AdamW", False, "push"),  # the world size
+        layout_digest(_as_groups(a), 2, "StableAdamW", True, "push"),  # optimizer and split mode
+        layout_digest(_as_groups(a), 2, "AdamW", False, "nccl"),  # the exchange
+    ]
+    assert base not in different and len(set(different)) == len(different)
