@@ -45,7 +45,7 @@ FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum per parameter of the bf16+Kahan kernels, from ncu captures of a
 # 336 M-parameter list (StableAdamW: both passes together); traffic is proportional to the parameter count, so a
 # step's traffic is this figure times its elements
-NCU_DRAM_BYTES_PER_PARAM = {"adamw": 17.83, "adam": 17.83, "lion": 13.83, "adan": 25.83, "stableadamw": 21.72}
+NCU_DRAM_BYTES_PER_PARAM = {"adamw": 17.83, "adam": 17.83, "lion": 13.83, "adan": 25.84, "stableadamw": 21.70}
 
 HYPER = dict(lr=3e-4, betas=(0.9, 0.99), weight_decay=1e-5, eps=1e-6, decouple_lr=True)
 
