@@ -143,7 +143,7 @@ def test_full_size_against_reference_foreach(cname, hyper, steps, keys):
                 assert not bool(bad.any()), f"{cname}: {name} of tensor {i}: {int(bad.sum())} elements more than 1 ulp apart"
 
 
-def _compare_with_reference(cname, hyper, steps, keys, shapes, scales, seed_base, label):
+def _compare_with_reference(cname, hyper, steps, keys, shapes, scales, seed_base, label, dtype=torch.bfloat16):
     """Steps `shapes` (one chunk of a parameter list) `steps` times under both implementations with the same
     seeded gradients and compares parameters and states; everything is freed on return."""
     import optimi
@@ -151,7 +151,7 @@ def _compare_with_reference(cname, hyper, steps, keys, shapes, scales, seed_base
     import optimi_b200
     from bench import make_params
 
-    mine = [p.requires_grad_(True) for p in make_params(shapes, "cuda", torch.bfloat16, seed=seed_base)]
+    mine = [p.requires_grad_(True) for p in make_params(shapes, "cuda", dtype, seed=seed_base)]
     theirs = [p.detach().clone().requires_grad_(True) for p in mine]
     with warnings.catch_warnings():
         warnings.simplefilter("ignore")
@@ -160,13 +160,14 @@ def _compare_with_reference(cname, hyper, steps, keys, shapes, scales, seed_base
     for step in range(steps):
         gen = torch.Generator(device="cuda").manual_seed(1000 * seed_base + step)
         for p, q, sc in zip(mine, theirs, scales):
-            g = torch.randn(p.shape, device="cuda", generator=gen).mul_(sc).to(torch.bfloat16)
+            g = torch.randn(p.shape, device="cuda", generator=gen).mul_(sc).to(dtype)
             p.grad = g
             q.grad = g.clone()  # the reference's foreach path clobbers its gradients
         opt_b200.step()
         opt_ref.step()
     torch.cuda.synchronize()
-    exact = cname != "StableAdamW"  # its per-tensor mean is summed in another order: 1 bf16 ulp
+    exact = cname != "StableAdamW"  # its per-tensor mean is summed in another order: 1 unit of the storage type
+    ulp = 2.0**-7 if dtype == torch.bfloat16 else 2.0**-10
     for i, (p, q) in enumerate(zip(mine, theirs)):
         pairs = [("param", p.detach(), q.detach())] + [(k, opt_b200.state[p][k], opt_ref.state[q][k]) for k in keys]
         for name, a, b in pairs:
@@ -174,7 +175,7 @@ def _compare_with_reference(cname, hyper, steps, keys, shapes, scales, seed_base
                 assert torch.equal(a, b), f"{cname}, {label}: {name} of tensor {i} {tuple(p.shape)} differs after {steps} steps"
             else:
                 scale = torch.maximum(a.float().abs(), b.float().abs()).clamp_min(1e-3)
-                bad = (a.float() - b.float()).abs() > scale * 2.0**-7
+                bad = (a.float() - b.float()).abs() > scale * ulp
                 assert not bool(bad.any()), f"{cname}, {label}: {name} of tensor {i}: {int(bad.sum())} elements more than 1 ulp apart"
     n = sum(p.numel() for p in mine)
     del mine, theirs, opt_ref, opt_b200
@@ -238,3 +239,26 @@ def test_llama_3b_list_adan_ranger_30_steps_against_reference(cname, hyper, keys
     scales = grad_scales(len(shapes), seed=0)
     n = _compare_with_reference(cname, hyper, 30, keys, shapes, scales, 7, "the 3 B list")
     assert n == sum(int(torch.Size(s).numel()) for s in shapes)
+
+
+FP16_RUNS = [
+    ("AdamW", dict(lr=3e-4, betas=(0.9, 0.99), weight_decay=1e-5, eps=1e-6, decouple_lr=True), ("exp_avg", "exp_avg_sq", "kahan_comp")),
+    ("Adan", dict(lr=3e-4, betas=(0.98, 0.92, 0.99), kahan_sum=True), ("exp_avg", "exp_avg_diff", "exp_avg_sq", "prev_grad", "kahan_comp")),
+    ("Lion", dict(lr=1e-4, betas=(0.9, 0.99), weight_decay=0.1), ("exp_avg", "kahan_comp")),
+]
+
+
+@pytest.mark.parametrize("cname,hyper,keys", FP16_RUNS, ids=[r[0] for r in FP16_RUNS])
+def test_float16_against_reference_foreach(cname, hyper, keys):
+    """The float16 kernels (11-bit significands: their own packed Kahan tail, the division shortcut's other operand
+    width, the IEEE square root) on the 1.1 B list, 10 steps, bit for bit against the unmodified reference's foreach path."""
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_dir, "optimi")):
+        pytest.skip("reference package not present beside the repository")
+    _need_free(40)
+    sys.path.insert(0, ref_dir)
+    sys.path.insert(0, ROOT)
+    from bench import WORKLOADS, grad_scales
+
+    shapes = WORKLOADS["llama-1.1b"]()
+    _compare_with_reference(cname, hyper, 10, keys, shapes, grad_scales(len(shapes), seed=0), 11, "the 1.1 B list in float16", dtype=torch.float16)
