@@ -270,3 +270,34 @@ def test_permuted_dense_parameter_steps_like_its_memory():
     p.grad = grads[0].t().contiguous()  # same shape, other strides
     with pytest.raises(RuntimeError, match="does not match its parameter"):
         a.step()
+
+
+def test_step_groups_in_any_order_equals_one_step():
+    """`step_groups` steps some parameter groups now and others later (each group has its own step counter); over
+    all groups it must leave exactly what one `step()` leaves, whatever the order."""
+    import optimi_b200
+
+    gen = torch.Generator().manual_seed(4)
+    shapes = [(257, 129), (4096,), (1000, 33), (7,)]
+    host = [(torch.randn(s, generator=gen) * 0.02).to(torch.bfloat16) for s in shapes]
+
+    def groups(ps):
+        return [{"params": ps[:1]}, {"params": ps[1:3], "weight_decay": 0.0, "lr": 1e-3}, {"params": ps[3:]}]
+
+    a = [torch.nn.Parameter(h.clone().cuda()) for h in host]
+    b = [torch.nn.Parameter(h.clone().cuda()) for h in host]
+    kw = dict(lr=3e-4, weight_decay=1e-2)
+    whole, pieces = optimi_b200.AdamW(groups(a), **kw), optimi_b200.AdamW(groups(b), **kw)
+    for it in range(4):
+        for p, q in zip(a, b):
+            g = (torch.randn(p.shape, generator=gen) * 1e-3).to(torch.bfloat16).cuda()
+            p.grad, q.grad = g.clone(), g.clone()
+        whole.step()
+        pieces.step_groups([2] if it % 2 else [1])
+        pieces.step_groups([0, 1] if it % 2 else [0, 2])
+    torch.cuda.synchronize()
+    for p, q in zip(a, b):
+        assert torch.equal(p.detach(), q.detach())
+        for k in ("exp_avg", "exp_avg_sq", "kahan_comp"):
+            assert torch.equal(whole.state[p][k], pieces.state[q][k])
+    assert [int(g["step"]) for g in pieces.param_groups] == [4, 4, 4]
