@@ -430,11 +430,17 @@ def run_b200_arm(args):
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node {args.gpus}")
     device = torch.device("cuda", local)
     torch.cuda.set_device(device)
-    dtype = {"bf16": torch.bfloat16, "fp16": torch.float16}[args.dtype]  # fp16: a secondary figure; the metric is quoted on bf16
+    # fp16 and fp32 are secondary figures; the metric is quoted on bf16
+    dtype = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[args.dtype]
     shapes = WORKLOADS[args.workload]()
     n_params = sum(numel(s) for s in shapes)
 
     cls_name, opt_kw, bytes_per_param, kernel_name = OPTIMIZERS[args.optimizer]
+    if args.dtype == "fp32":
+        # float32 has no Kahan buffer: one 4-byte stream fewer in each direction than the 2-byte count, all streams 4 bytes
+        bytes_per_param = (bytes_per_param - 4) * 2
+        opt_kw = {k: v for k, v in opt_kw.items() if k != "kahan_sum"}
+        kernel_name = kernel_name.replace("bf16", "f32").replace("kahan,", "").replace("<kahan>", "")
     opt_cls = getattr(optimi_b200, cls_name)
     params = [p.requires_grad_(True) for p in make_params(shapes, device, dtype, seed=0)]
     if world == 1:
@@ -665,7 +671,7 @@ def run_b200_arm(args):
     # roofline of the step kernel is taken from the local-only steps timed above
     kernel_ms = local_step_ms if local_step_ms is not None else step_ms_max
     achieved = bytes_per_param * n_local / (kernel_ms * 1e-3) / 1e9
-    ncu_bpp = NCU_DRAM_BYTES_PER_PARAM.get(args.optimizer)
+    ncu_bpp = NCU_DRAM_BYTES_PER_PARAM.get(args.optimizer) if args.dtype == "bf16" else None  # the captures are of the bf16 kernels
     traffic = ncu_bpp * n_local / kernel_launches_per_step if ncu_bpp is not None else None
     roofline = {
         "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": traffic,
@@ -746,6 +752,10 @@ def run_b200_arm(args):
                 "ms_per_step": e2e_s * 1e3, "steps": e2e_steps, "overlap": e2e_overlap},
         "gpu_launches": int(launches), "clocks": clocks.result, "library": os.path.relpath(_lib.LIB_PATH, ROOT),
     }  # fmt: skip
+    if args.dtype != "bf16":  # say what was stepped where the line names the workload
+        label = "fp16+Kahan" if args.dtype == "fp16" else "fp32 (no Kahan buffer)"
+        line["metric"] = line["metric"].replace("bf16-Kahan", label)
+        line["config"]["workload"] = line["config"]["workload"].replace("bf16+Kahan", label)
     print(json.dumps(line))
 
 
@@ -865,7 +875,7 @@ def main():
     ap.add_argument("--impl", default="optimi_b200", choices=["optimi_b200", "reference"])
     ap.add_argument("--workload", default="llama3-8b", choices=sorted(WORKLOADS) + ["gpt-gradient-release"])
     ap.add_argument("--optimizer", default="adamw", choices=sorted(OPTIMIZERS), help="default: the headline AdamW")
-    ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp16"], help="storage type of parameters, gradients and states (the metric is quoted on bf16)")
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp16", "fp32"], help="storage type of parameters, gradients and states (the metric is quoted on bf16)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-reference-gpu", action="store_true", help="skip timing the reference's CUDA back ends on the 1.1 B list (N=1)")
     ap.add_argument("--reduce-grads", action="store_true", help="N>1 with the push exchange: also average the ranks' gradients inside the step kernel")

@@ -384,6 +384,14 @@ class OptimiOptimizer(Optimizer):
         self._grad_factor, self._grad_factor_once = self._clip_out[:1], not capturing
         return self._clip_out[1].clone()  # the two-float buffer is reused by the next call
 
+    def _index_tensor(self, indices: tuple, device: torch.device) -> Tensor:
+        """A device tensor of `indices`, kept for the next call (the same few index sets recur every step)."""
+        cache = self.__dict__.setdefault("_index_tensors", {})
+        t = cache.get((indices, device))
+        if t is None:
+            t = cache[(indices, device)] = torch.tensor(indices, dtype=torch.int64, device=device)
+        return t
+
     @torch.no_grad()
     def _clip_from_sumsq(self, tensors: list[Tensor], owners: list[int], dtypes: list[torch.dtype], max_norm: float,
                          reduce_sums: Callable[[Tensor], None] | None = None) -> Tensor:  # fmt: skip
@@ -426,13 +434,13 @@ class OptimiOptimizer(Optimizer):
                 _lib.check(_lib.LIB.optimi_b200_grad_sumsq(len(grads), ptrs.ptr, numels_arg, _lib.DTYPE_CODE[dtype], piece.data_ptr(),
                                                           ws.data_ptr(), ws.numel(), stream_ptr))  # fmt: skip
                 # a whole tensor has at most one piece in `tensors`, so this is a plain scatter
-                sumsq[torch.tensor([owners[i] for i in idx], device=device)] = piece
+                sumsq[self._index_tensor(tuple(owners[i] for i in idx), device)] = piece
             if reduce_sums is not None:
                 reduce_sums(sumsq)
             norms = torch.zeros(n_full, dtype=torch.float32, device=device)
             kinds = sorted(set(dtypes), key=str)
             for dtype in kinds:
-                sel = torch.tensor([j for j, d in enumerate(dtypes) if d == dtype], device=device)
+                sel = self._index_tensor(tuple(j for j, d in enumerate(dtypes) if d == dtype), device)
                 sub = sumsq[sel].contiguous()
                 out = torch.empty(sub.numel(), dtype=torch.float32, device=device)
                 _lib.check(_lib.LIB.optimi_b200_grad_norms_from_sumsq(sub.numel(), sub.data_ptr(), _lib.DTYPE_CODE[dtype], out.data_ptr(), stream_ptr))
