@@ -8,7 +8,7 @@
 // kThreads * U vectors (16 bytes each); one 128-thread block owns one tile, issues ALL of its loads
 // up front (U vectors per stream per thread), computes, stores and exits.  Millions of short-lived
 // blocks keep every SM's memory pipeline full without a persistent loop, and a register budget
-// around 50 leaves ten blocks resident per SM.  Block b finds its tensor through a 256-entry
+// of 40 leaves twelve blocks resident per SM.  Block b finds its tensor through a 256-entry
 // coarse index over the block range plus a short forward walk over the prefix sum of block counts
 // (a plain binary search over the table cost 10-20 % of the step: every probe is a dependent,
 // dynamically indexed read of kernel-parameter space).
