@@ -88,3 +88,36 @@ def test_all_ranks_played_on_one_gpu_equal_unsharded_step_on_mean_gradient(which
     for r in range(world):
         assert torch.equal(params[r, :total], twin.detach()), f"rank {r}'s copy differs from the unsharded step on the mean gradient"
     assert bool((grads[:, total:] == 0).all()) and bool((params[:, total:] == 0).all()), "something was written past the lists"
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_push_only_with_all_ranks_on_one_gpu(world):
+    """The plain sharded step (gradients already reduced, the step kernel only pushes its updated range to up to
+    seven peers): after all ranks have been played, every copy equals the unsharded step."""
+    import optimi_b200
+    import optimi_b200.functional as F
+    from optimi_b200._lib import peer_push
+
+    per_rank = 4096 * 2 + 264
+    total = per_rank * world
+    dev, dt = torch.device("cuda"), torch.bfloat16
+    gen = torch.Generator().manual_seed(world)
+    init = (torch.randn(total, generator=gen) * 0.02).to(dt)
+    params = init.to(dev).repeat(world, 1).contiguous()
+    row_bytes = total * 2
+    st = [[torch.zeros(per_rank, dtype=dt, device=dev) for _ in range(3)] for _ in range(world)]
+    steps = [torch.tensor(0, dtype=torch.int32) for _ in range(world)]
+    twin = torch.nn.Parameter(init.clone().to(dev))
+    plain = optimi_b200.AdamW([twin], lr=3e-4, weight_decay=1e-2)
+    for _ in range(3):
+        grad = (torch.randn(total, generator=gen) * 1e-3).to(dt).to(dev)
+        for r in range(world):
+            lo, hi = r * per_rank, (r + 1) * per_rank
+            with torch.no_grad(), peer_push([(s - r) * row_bytes for s in range(world) if s != r]):
+                F.adamw([params[r, lo:hi]], [grad[lo:hi]], [st[r][0]], [st[r][1]], [st[r][2]], lr=3e-4, beta1=0.9, beta2=0.99,
+                        weight_decay=1e-2, eps=1e-6, step=steps[r], kahan_sum=True)
+        twin.grad = grad
+        plain.step()
+    torch.cuda.synchronize()
+    for r in range(world):
+        assert torch.equal(params[r], twin.detach()), f"rank {r}'s copy differs from the unsharded step"
