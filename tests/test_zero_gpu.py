@@ -7,7 +7,9 @@ memory handshake dominate the cost of a case, and a machine with eight GPUs is n
 thirteen times.  Each test then only looks up its own case's verdict.
 
 Two ranks by default; ``OPTIMI_TEST_WORLD=4`` (or 8) on a machine with that many GPUs runs the same
-cases over more ranks (the gradient-mean kernels are compiled per rank bound 2, 4, 8).
+cases over more ranks (the gradient-mean kernels are compiled per rank bound 2, 4, 8).  The session takes
+about half a minute over two ranks and a minute and a quarter over four (start-up and the symmetric-memory
+handshakes grow with the rank count); give eight ranks ten minutes.
 """
 
 import datetime
